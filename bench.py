@@ -1,0 +1,409 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2] [--no-suite]
+
+Headline workload (N = 1): BASELINE config[1], the W4A16 decode GEMM M=16, K=4096, N=4096, group 128,
+zero point 8, fp16.  One problem is only 8.9 MB, far below the L2 size, so a *step* is one pass over
+LAYERS = 32 distinct weight sets of that shape (285 MB > L2): 32 kernel launches, replayed from one CUDA
+graph.  `value` is algorithmic bytes (each input read once, output written once) over device time, GB/s,
+whole job over all ranks.  With N > 1 the headline config does not shard ("replicas only"): every rank
+runs its own replica (weak scaling).  The sharded configurations (config 4 by batch, config 5 by weight
+columns with an all-gather of outputs) and the other single-GPU configurations are measured in the same
+run and reported under `suite`.
+
+`--impl reference` times the reference's torch CPU program for this path (the restatement in oracle/,
+all host threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+LAYERS = 32
+CFG2 = dict(M=16, K=4096, N=4096, group=128)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the committed ncu
+# summary under profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def w4a16_bytes(M, K, N, group, out_bytes=2, a_bytes=2):
+    return K * N // 2 + 2 * (K // group) * N + a_bytes * M * K + out_bytes * M * N
+
+
+def w8a8_bytes(batch, M, K, N, out_bytes=2):
+    return batch * (M * K + K * N + 4 * M + 4 * N + out_bytes * M * N)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {}
+        for n in dir(nv):
+            if n.startswith("nvmlClocksEventReason") or n.startswith("nvmlClocksThrottleReason"):
+                v = getattr(nv, n)
+                if isinstance(v, int) and v not in (0,):
+                    names.setdefault(v, n.replace("nvmlClocksEventReason", "").replace("nvmlClocksThrottleReason", ""))
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(
+            nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                if get_reasons is not None:
+                    r = get_reasons(self.h)
+                    for bit, name in names.items():
+                        if r & bit and bit & (bit - 1) == 0 and name not in ("GpuIdle", "All", "None"):
+                            self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join(timeout=2)
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def dist_setup(n_gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return world, rank, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms, world):
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def timed(fn_step, steps, warmup, world):
+    """W untimed steps, then exactly K steps between barrier + synchronize, CUDA events, max over ranks."""
+    for _ in range(warmup):
+        fn_step()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn_step()
+    e1.record()
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world)
+
+
+def make_graph_step(launch_all, stream):
+    """Capture one step (all its launches) in a CUDA graph on `stream`; fall back to eager launches."""
+    try:
+        with torch.cuda.stream(stream):
+            launch_all()  # warm: workspaces for this stream exist before capture
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            launch_all()
+        return (lambda: g.replay()), "cuda_graph"
+    except Exception as exc:  # pragma: no cover - depends on driver behaviour
+        sys.stderr.write(f"[bench] CUDA graph capture failed ({exc}); timing eager launches\n")
+        return launch_all, "eager"
+
+
+# ----------------------------------------------------------------------------------------- our arm
+def headline_inputs(seed0):
+    from oracle import qgemm_oracle as oc  # input generator only (shared with the tests)
+    layers = []
+    for l in range(LAYERS):
+        A, P, S = oc.make_w4a16_inputs(CFG2["M"], CFG2["K"], CFG2["N"], "float16", CFG2["group"], seed=seed0 + l)
+        layers.append((A.pin_memory(), P.pin_memory(), S.pin_memory()))
+    return layers
+
+
+def run_ours(args):
+    import tilelang_ascend_b200 as q
+
+    world, rank, local = dist_setup(args.gpus)
+    peaks, peaks_src = load_peaks()
+    host_layers = headline_inputs(1000 * rank)
+    dev_layers = [tuple(t.cuda(non_blocking=True) for t in lay) for lay in host_layers]
+    torch.cuda.synchronize()
+    outs = [None] * LAYERS
+
+    def launch_all():
+        for i, (A, P, S) in enumerate(dev_layers):
+            outs[i] = q.w4a16_gemm(A, P, S, 8, CFG2["group"])
+
+    stream = torch.cuda.Stream()
+    step, launch_mode = make_graph_step(launch_all, stream)
+    bytes_step = LAYERS * w4a16_bytes(**CFG2)
+    with torch.cuda.stream(stream):
+        with ClockSampler(local) as clk:
+            ms = timed(step, args.steps, args.warmup, world)
+            # keep the sampler fed with the same work for a little longer: the timed region is short
+            t_end = time.time() + 0.25
+            while time.time() < t_end:
+                step()
+            torch.cuda.synchronize()
+    value = world * bytes_step * args.steps / (ms * 1e-3) / 1e9
+    ms_per_step = ms / args.steps
+    launch_us = ms_per_step * 1e3 / LAYERS
+    achieved = w4a16_bytes(**CFG2) / (launch_us * 1e-6) / 1e9
+
+    # end to end through the reference-facing wrapper: host tensors in, host tensor out, every step
+    wrapper = q.dequant_gemm_fp16_wrapper(CFG2["M"], CFG2["N"], CFG2["K"], 128, 256, 64, "float16", "float16")
+
+    def e2e_step():
+        for (A, P, S) in host_layers:
+            wrapper(A, P, S, 8, CFG2["group"])
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_ms = timed(e2e_step, e2e_steps, 1, world)
+    h2d = LAYERS * sum(t.numel() * t.element_size() for t in host_layers[0])
+    d2h = LAYERS * CFG2["M"] * CFG2["N"] * 2
+    e2e_value = world * bytes_step * e2e_steps / (e2e_ms * 1e-3) / 1e9
+
+    suite = None
+    if not args.no_suite:
+        suite = run_suite(q, world, rank, peaks)
+
+    cpu_base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_base = cpu_baseline(sample_seconds=12.0)
+
+    if rank == 0:
+        line = {
+            "metric": "w4a16_decode_gbs", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 (int4 weights, fp32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": "BASELINE configs[1]: W4A16 dequantize_gemm decode M=16 K=4096 N=4096 group=128 zero=8 fp16; "
+                                   f"one step = {LAYERS} distinct weight sets ({LAYERS * 8.9:.0f} MB > L2, so no L2 flush needed)",
+                       "layers_per_step": LAYERS, "launch": launch_mode,
+                       "multi_gpu": "replicas only for this config; sharded configs are under suite"},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "kernel": "w4a16_gemm_kernel<16>", "us_per_launch": round(launch_us, 3),
+                         "algorithmic_bytes_per_launch": w4a16_bytes(**CFG2), "peak_source": peaks_src + " (copy)"},
+            "e2e": {"value": round(e2e_value, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "api": "dequant_gemm_fp16_wrapper(CPU tensors) -> CPU tensor"},
+            "gpu_launches": world * LAYERS * args.steps,
+            "clocks": clk.summary(),
+        }
+        if cpu_base is not None:
+            line["cpu_baseline"] = cpu_base
+        if suite is not None:
+            line["suite"] = suite
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def _time_rotating(fn_of_idx, n_sets, iters, world):
+    """Median-free simple timing: `iters` launches cycling over `n_sets` input sets, device time per launch."""
+    for i in range(min(3, iters)):
+        fn_of_idx(i % n_sets)
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn_of_idx(i % n_sets)
+    e1.record()
+    barrier(world)
+    return max_over_ranks(e0.elapsed_time(e1), world) / iters
+
+
+def run_suite(q, world, rank, peaks):
+    """The other BASELINE configurations, sharded where they shard.  Device-resident inputs, CUDA events,
+    max over ranks; inputs either exceed L2 or rotate over enough copies to exceed it."""
+    from oracle import qgemm_oracle as oc  # input generators only
+    from tilelang_ascend_b200.dist import ColumnShardedW4A16, shard_batches
+    int8_peak = 2 * peaks["bf16_tflops"]  # no measured int8 figure: 2x the measured bf16 burst
+    res = []
+
+    if world == 1:
+        A, B, sa, sb = [t.cuda() for t in oc.make_config_inputs("cfg1")]
+        ms = _time_rotating(lambda i: q.quant_matmul(A, B, sb, scale_a=sa, out_dtype="float16"), 1, 50, world)
+        ops = 2 * 256 * 1024 * 1024
+        res.append({"config": "cfg1 W8A8 1x256x1024x1024 fp16 (L2-warm, launch-bound)", "ms": round(ms, 5),
+                    "tops": round(ops / ms / 1e9, 2)})
+        del A, B
+        A, B, sa, sb = [t.cuda() for t in oc.make_config_inputs("cfg3")]
+        ms = _time_rotating(lambda i: q.quant_matmul(A, B, sb, scale_a=sa, out_dtype="bfloat16"), 1, 20, world)
+        ops = 2 * 4096 * 4096 * 14336
+        res.append({"config": "cfg3 W8A8 4096x4096x14336 bf16", "ms": round(ms, 5), "tops": round(ops / ms / 1e9, 1),
+                    "frac_of_2x_measured_bf16": round(ops / ms / 1e9 / int8_peak, 4)})
+        del A, B
+
+    # config 4: batch sharded, no collective
+    A, B, sa, sb = oc.make_config_inputs("cfg4")
+    A, B, sa, sb = [t.cuda() for t in shard_batches([A, B, sa, sb], world, rank)]
+    ms = _time_rotating(lambda i: q.quant_matmul(A, B, sb, scale_a=sa, out_dtype="bfloat16"), 1, 20, world)
+    ops = 2 * 16 * 512 * 7168 * 2048
+    res.append({"config": f"cfg4 W8A8 16x512x7168x2048 bf16, batch sharded over {world}", "ms": round(ms, 5),
+                "tops": round(ops / ms / 1e9, 1), "frac_of_2x_measured_bf16": round(ops / ms / 1e9 / (world * int8_peak), 4)})
+    del A, B
+
+    # config 5: weight columns sharded, all-gather of outputs; two weight copies so reads stay L2-cold
+    K, N = 8192, 28672
+    _, P, S = oc.make_config_inputs("cfg5", M=1)
+    layers = [ColumnShardedW4A16(P, S, 8, 128).to("cuda"), ColumnShardedW4A16(P.flip(0).contiguous(), S, 8, 128).to("cuda")]
+    del P
+    for M in (1, 8, 64, 512, 4096):
+        g = torch.Generator().manual_seed(M)
+        A = torch.randn((M, K), generator=g).to(torch.bfloat16).cuda()
+        iters = 20 if M <= 512 else 6
+        ms_c = _time_rotating(lambda i: layers[i % 2].forward(A, gather=False), 2, iters, world)
+        ms_g = _time_rotating(lambda i: layers[i % 2].forward(A, gather=True), 2, iters, world) if world > 1 else ms_c
+        by = w4a16_bytes(M, K, N, 128)
+        fl = 2 * M * K * N
+        entry = {"config": f"cfg5 W4A16 M={M} K=8192 N=28672 bf16, columns sharded over {world}",
+                 "ms_compute": round(ms_c, 5), "ms_with_allgather": round(ms_g, 5),
+                 "gbs": round(by / ms_c / 1e6, 1), "tflops": round(fl / ms_c / 1e9, 1)}
+        if M <= 64:
+            entry["frac_of_measured_hbm"] = round(by / ms_c / 1e6 / (world * peaks["hbm_gbs"]), 4)
+        else:
+            entry["frac_of_measured_bf16"] = round(fl / ms_c / 1e9 / (world * peaks["bf16_tflops"]), 4)
+        res.append(entry)
+    return res
+
+
+# ------------------------------------------------------------------------------- CPU reference arm
+def cpu_baseline(sample_seconds=12.0):
+    """The reference's torch CPU program for the headline config (restated in oracle/), all host threads.
+
+    Sample: whole layers of the headline workload (unpack, (q - 8) * s dequant, fp32 matmul, cast) for
+    about `sample_seconds` seconds."""
+    from oracle import qgemm_oracle as oc
+    torch.set_num_threads(os.cpu_count() or 1)
+    A, P, S = oc.make_w4a16_inputs(CFG2["M"], CFG2["K"], CFG2["N"], "float16", CFG2["group"], seed=0)
+    oc.dequant_gemm_fp16_ref(A, P, "float16", S, 8, CFG2["group"])
+    t0, n = time.perf_counter(), 0
+    while True:
+        oc.dequant_gemm_fp16_ref(A, P, "float16", S, 8, CFG2["group"])
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt > sample_seconds or n >= 400:
+            break
+    gbs = n * w4a16_bytes(**CFG2) / dt / 1e9
+    return {"value": round(gbs, 4), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n} layers of configs[1] (M=16 K=4096 N=4096) in {dt:.1f} s: vectorised unpack + (q-8)*s + fp32 matmul + cast",
+            "ms_per_layer": round(dt / n * 1e3, 2)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import qgemm_oracle as oc
+    torch.set_num_threads(os.cpu_count() or 1)
+    A, P, S = oc.make_w4a16_inputs(CFG2["M"], CFG2["K"], CFG2["N"], "float16", CFG2["group"], seed=0)
+
+    def step():  # one layer per step: a bounded sample of the 32-layer step
+        oc.dequant_gemm_fp16_ref(A, P, "float16", S, 8, CFG2["group"])
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    gbs = args.steps * w4a16_bytes(**CFG2) / dt / 1e9
+    cores = torch.get_num_threads()
+    sample = f"one layer of configs[1] per step ({args.steps} steps, {dt:.2f} s): the reference's torch CPU program restated in oracle/"
+    line = {
+        "impl": "reference", "metric": "w4a16_decode_gbs", "value": round(gbs, 4), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 (int4 weights, fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": "BASELINE configs[1]: W4A16 dequantize_gemm decode M=16 K=4096 N=4096 group=128 zero=8 fp16; "
+                               "CPU sample: one layer per step", "layers_per_step": 1},
+        "cpu_baseline": {"value": round(gbs, 4), "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(gbs, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-suite", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,134 @@
+/*
+ * qgemm.h — C ABI of libqgemm.so: quantized GEMM operators for NVIDIA B200 (sm_100a).
+ *
+ * This is the drop-in boundary for the quantized-GEMM operators of tile-ai/tilelang-ascend
+ * (examples/quant_batch_matmul, examples/dequantize_gemm, packing as in tilelang/quantize).
+ * In the reference every compiled operator is a shared object that exports
+ *     extern "C" void call(uint8_t* arg0, ..., <int64 dynamic dims>, aclrtStream stream)
+ * (src/target/codegen_ascend.cc:1061-1112), called through ctypes with raw device pointers in
+ * parameter order, outputs and workspaces included, stream last
+ * (tilelang/jit/adapter/cython/cython_wrapper.pyx:143-197).  The entry points below keep that
+ * convention — plain device pointers, sizes as int64, stream last, asynchronous launch, no host
+ * synchronisation — and add what the reference's CUDA-flavoured wrapper template defines and its
+ * NPU build leaves out (tilelang/jit/adapter/wrapper.py:30-50): an init call, an int return code
+ * and a last-error string.
+ *
+ * Rules common to all entry points
+ *  - All pointers are device pointers on the current CUDA device, tensors are contiguous row-major.
+ *  - Nothing is allocated or freed on the device and no pointer is retained after return.
+ *  - Return value 0 = launched; non-zero = rejected before any launch, qgemm_last_error() says why.
+ *  - `status` (nullable) is a device uint32 the caller zeroes; a kernel whose bounded wait expired
+ *    stores a non-zero code there (see QGEMM_ST_*), drains and returns normally.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ */
+#ifndef QGEMM_H_
+#define QGEMM_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QGEMM_DT_F16 0
+#define QGEMM_DT_BF16 1
+#define QGEMM_DT_I32 2
+
+#define QGEMM_B_KN 0 /* B stored [batch, K, N], N contiguous (examples/quant_batch_matmul) */
+#define QGEMM_B_NK 1 /* B stored [batch, N, K], K contiguous (examples/deepseek_v4/int8_gemm.py:58) */
+
+#define QGEMM_ST_OK 0
+#define QGEMM_ST_TIMEOUT_PRODUCER 1
+#define QGEMM_ST_TIMEOUT_MMA 2
+#define QGEMM_ST_TIMEOUT_EPILOGUE 3
+#define QGEMM_ST_TIMEOUT_DEQUANT 4
+#define QGEMM_ST_TIMEOUT_DRAIN 5
+
+/* Library version (major * 1000 + minor). */
+int qgemm_version(void);
+
+/* Per-device set-up (kernel attributes, driver entry points) for the current device.  Optional:
+ * every entry point does it on first use.  Replaces `int init()` of
+ * tilelang/jit/adapter/wrapper.py:36-43. */
+int qgemm_init(void);
+
+/* Message of the last non-zero return on the calling thread.  Replaces `get_last_error()` of
+ * tilelang/jit/adapter/wrapper.py:30-34. */
+const char* qgemm_last_error(void);
+
+/* Per-wait limit of the kernels' bounded waits, in milliseconds (default 2000). */
+void qgemm_set_wait_limit_ms(uint32_t ms);
+
+/*
+ * W8A8 quantized (batched) matmul.  Replaces the compiled `call` of
+ * simple_quant_batch_matmul / simple_quant_matmul
+ * (examples/quant_batch_matmul/example_quant_batch_matmul.py:17-91, example_quant_matmul.py:17-90)
+ * and of the two-scale kernel examples/deepseek_v4/int8_gemm.py:35-104.
+ *
+ *   acc[b,m,n] = sum_k int32(A[b,m,k]) * int32(B[b,k,n])                          (exact)
+ *   C[b,m,n]   = cast_out( float(acc) [* scale_a[..m]] * scale_b[..n] )            (fp32, RN casts)
+ *
+ * A: [batch, M, K] int8.  B: [batch, K, N] (QGEMM_B_KN) or [batch, N, K] (QGEMM_B_NK) int8.
+ * scale_b: fp32, scale_b_len = 1, N (shared by all batches) or batch*N.
+ * scale_a: nullable fp32, scale_a_len = 0, M (shared) or batch*M.
+ * C: [batch, M, N] of out_dtype (F16 / BF16), or NULL when only accumulators are wanted; with
+ *    out_dtype = QGEMM_DT_I32, C receives the raw int32 accumulators and the scales are ignored.
+ * acc_out: nullable [batch, M, N] int32 — the reference's `workspace_1` (example_quant_batch_matmul.py:42),
+ *    filled with the raw accumulators when given.
+ * Unbatched operators pass batch = 1.  Requires K % 16 == 0 and N % 16 == 0.
+ */
+int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const float* scale_a, void* C,
+               int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t scale_b_len,
+               int64_t scale_a_len, int out_dtype, int b_layout, uint32_t* status, void* stream);
+
+/* Bytes of scratch memory qgemm_w4a16 needs for this problem on the current device (split-K partial
+ * sums and arrival counters).  The first use of a scratch buffer must find its first
+ * qgemm_w4a16_counter_bytes() bytes zeroed; the kernel leaves them zero.  Two launches that may
+ * overlap on the device must not share a scratch buffer. */
+int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int64_t qgemm_w4a16_counter_bytes(void);
+
+/*
+ * W4A16 dequantize-GEMM.  Replaces dequant_gemm_fp16_wrapper's host unpack + compiled fp16 GEMM
+ * (examples/dequantize_gemm/example_dequant_gemm_fine_grained.py:69-115,176-223); the scaled form
+ * follows tilelang/quantize/utils.py:33,46 and zero mode "original" of tilelang/quantize/lop3.py:135-175.
+ *
+ *   q[n,k]  = (B_packed[n, k/2] >> 4*(k%2)) & 0xF            (low nibble = even k)
+ *   W[n,k]  = scales ? half(q - zero) * scales[k/group, n] : half(q)
+ *   C[m,n]  = cast_out( sum_k float(A[m,k]) * float(W[n,k]) )   (fp32 accumulation)
+ *
+ * A: [M, K] of a_dtype (F16 / BF16; bf16 is converted to f16 on the fly, as the reference wrapper does,
+ *    example_dequant_gemm_fine_grained.py:211-214).  B_packed: [N, K/2] uint8.
+ * scales: nullable [K/group, N] fp16; with scales == NULL `zero` and `group` are ignored.
+ * C: [M, N] of out_dtype (F16 / BF16).  workspace: scratch of at least qgemm_w4a16_workspace_bytes().
+ * Requires K % 32 == 0, N % 8 == 0, 0 <= zero <= 15, and group dividing 256, a multiple of 256, or >= K
+ * (with K % group == 0).
+ */
+int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
+                void* workspace, int64_t workspace_bytes, int64_t M, int64_t N, int64_t K, int a_dtype,
+                int out_dtype, uint32_t* status, void* stream);
+
+/*
+ * int4 -> int8 unpack of a packed weight matrix into a caller-provided [N, K] int8 buffer: the
+ * on-device form of torch_unpack_uint4_to_int8 (example_dequant_gemm_fine_grained.py:35-57,
+ * signed_nibbles = 0) and of the vector-core unpack stage of w4a8_gemm_cv
+ * (examples/dequantize_gemm/example_dequant_gemm_w4a8.py:69-106, signed_nibbles = 1, two's complement).
+ */
+int qgemm_unpack_int4(const uint8_t* B_packed, int8_t* out, int64_t N, int64_t K, int signed_nibbles,
+                      void* stream);
+
+/*
+ * W4A8 / int8-mode dequantize-GEMM: C[m,n] = sum_k int32(A[m,k]) * int32(unpack(qB)[n,k]), exact.
+ * Replaces kernel(A, qB, workspace, C) of w4a8_gemm_cv (example_dequant_gemm_w4a8.py:25-121; same
+ * caller-provided int8 [N, K] workspace) and dequant_gemm_int8_wrapper
+ * (example_dequant_gemm_fine_grained.py:226-266).  C is [M, N] int32 (out_dtype must be QGEMM_DT_I32;
+ * the reference wrapper casts to other types on the host afterwards, :263).  Requires K % 32 == 0
+ * and N % 16 == 0.
+ */
+int qgemm_w4a8(const int8_t* A, const uint8_t* qB, int8_t* workspace, void* C, int64_t M, int64_t N, int64_t K,
+               int signed_nibbles, int out_dtype, uint32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QGEMM_H_ */

@@ -1,0 +1,212 @@
+"""GPU parity tests for the W4A16 / W4A8 paths: CUDA kernels (through libqgemm.so) against the CPU oracle.
+
+Bars: fp16/bf16 outputs within rtol = atol = 1e-2
+(examples/dequantize_gemm/example_dequant_gemm_fine_grained.py:341-344); int32 outputs exact (:373-374,
+examples/dequantize_gemm/example_dequant_gemm_w4a8.py:182).  The kernel accumulates exact f16 x f16
+products in fp32 in a different order than the CPU matmul, so float results are close, not identical.
+"""
+import pytest
+import torch
+
+from oracle import qgemm_oracle as oc
+
+pytestmark = pytest.mark.gpu
+
+
+def _q():
+    import tilelang_ascend_b200 as q
+    return q
+
+
+def _close(C, ref):
+    assert C.dtype == ref.dtype
+    torch.testing.assert_close(C.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("name,dt", [("dq_f16", "float16"), ("dq_bf16", "bfloat16")])
+def test_golden_unscaled(golden, name, dt):
+    """Reference-produced vectors of ref_program_fp16 (unsigned nibbles, no scale, no zero point)."""
+    q = _q()
+    bf = ("A", "C") if dt == "bfloat16" else ()
+    c = golden.case(name, bf16=bf)
+    M, K = c["A"].shape
+    N = c["packed"].shape[0]
+    if K % 32 != 0 or N % 8 != 0:
+        pytest.skip("shape below the kernel's granularity")
+    w = q.dequant_gemm_fp16_wrapper(M, N, K, 128, 256, 64, dt, dt)
+    C = w(c["A"], c["packed"])  # CPU in -> CPU out, like the reference wrapper
+    assert not C.is_cuda
+    _close(C, c["C"])
+
+
+def test_reference_known_answer_through_kernel():
+    """The reference's nibble-order vector [[0x12, 0x34]] -> [2, 1, 4, 3], observed through the GEMM:
+    with A = identity rows the output row m is column m of the unpacked weights."""
+    q = _q()
+    K, N = 32, 8
+    packed = torch.zeros(N, K // 2, dtype=torch.uint8)
+    packed[0, 0], packed[0, 1] = 0x12, 0x34
+    A = torch.eye(K, dtype=torch.float16)[:4]
+    C = q.w4a16_gemm(A.cuda(), packed.cuda()).cpu()
+    assert C[:, 0].tolist() == [2.0, 1.0, 4.0, 3.0]
+    assert torch.equal(C.float(), oc.unpack_uint4(packed).float().t()[:4])
+
+
+W4_SHAPES = [
+    # M, K, N, group
+    (16, 256, 128, 128),
+    (1, 32, 8, 32),
+    (5, 96, 40, 32),
+    (16, 1024, 256, 128),
+    (8, 4096, 512, 128),
+    (33, 640, 264, 64),
+    (64, 2048, 384, 128),
+    (100, 512, 136, 256),
+    (256, 1024, 256, 128),
+    (300, 768, 520, -1),
+]
+
+
+@pytest.mark.parametrize("M,K,N,group", W4_SHAPES)
+@pytest.mark.parametrize("dt", ["float16", "bfloat16"])
+def test_scaled_against_oracle(M, K, N, group, dt):
+    q = _q()
+    g = K if group == -1 else group
+    A, packed, scales = oc.make_w4a16_inputs(M, K, N, dt, g, seed=M + N)
+    ref = oc.dequant_gemm_fp16_ref(A, packed, dt, scales, 8, g)
+    C = q.w4a16_gemm(A.cuda(), packed.cuda(), scales.cuda(), 8, group)
+    _close(C, ref)
+    # a second, tighter bar than the reference's: error relative to the output scale
+    err = (C.cpu().float() - ref.float()).abs().max().item()
+    assert err <= 2e-2 * max(1.0, ref.float().abs().max().item()) * (1 if dt == "float16" else 4)
+
+
+@pytest.mark.parametrize("M,K,N", [(16, 512, 128), (256, 256, 256), (512, 512, 512)])
+def test_unscaled_reference_semantics(M, K, N):
+    """scales=None: raw unsigned nibble values, exactly the reference example (its 256^3 / 512^3 ladder)."""
+    q = _q()
+    g = torch.Generator().manual_seed(0)
+    A = torch.randn(M, K, generator=g).half()
+    packed = torch.randint(0, 255, (N, K // 2), dtype=torch.uint8, generator=g)
+    w = q.dequant_gemm_fp16_wrapper(M, N, K, 128, 256, 64)
+    C = w(A.cuda(), packed.cuda())
+    assert C.is_cuda
+    _close(C, oc.dequant_gemm_fp16_ref(A, packed, "float16"))
+
+
+def test_dequant_is_exact_via_identity_activations():
+    """With A = I (K x K) the GEMM returns W^T: every dequantised weight must equal the oracle's fp16 value
+    bit for bit ((q - 8) is exact, the product with the scale rounds once)."""
+    q = _q()
+    K, N = 256, 136
+    _, packed, scales = oc.make_w4a16_inputs(1, K, N, "float16", 128, seed=3)
+    A = torch.eye(K, dtype=torch.float16)
+    C = q.w4a16_gemm(A.cuda(), packed.cuda(), scales.cuda(), 8, 128).cpu()
+    W = oc.dequant_weight_ref(packed, scales, 8, 128)  # [N, K]
+    assert torch.equal(C, W.t())
+    for zero in (0, 3, 15):
+        C = q.w4a16_gemm(A.cuda(), packed.cuda(), scales.cuda(), zero, 128).cpu()
+        assert torch.equal(C, oc.dequant_weight_ref(packed, scales, zero, 128).t())
+
+
+def test_split_k_is_deterministic_and_counters_stay_clean():
+    q = _q()
+    A, packed, scales = oc.make_config_inputs("cfg2")
+    Ad, Pd, Sd = A.cuda(), packed.cuda(), scales.cuda()
+    ref = oc.dequant_gemm_fp16_ref(A, packed, "float16", scales, 8, 128)
+    outs = [q.w4a16_gemm(Ad, Pd, Sd, 8, 128) for _ in range(5)]
+    _close(outs[0], ref)
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+
+
+@pytest.mark.parametrize("M", [1, 8, 64])
+def test_config5_decode_full_size(M):
+    """BASELINE config 5 decode shapes at full size (K = 8192, N = 28672, bf16): a band of output columns
+    against the oracle plus linearity in A over the whole output (f(A) + f(2A) == f(3A) up to rounding)."""
+    q = _q()
+    A, packed, scales = oc.make_config_inputs("cfg5", M=M)
+    Ad, Pd, Sd = A.cuda(), packed.cuda(), scales.cuda()
+    C = q.w4a16_gemm(Ad, Pd, Sd, 8, 128)
+    cols = torch.cat([torch.arange(0, 256), torch.arange(14000, 14200), torch.arange(28672 - 200, 28672)])
+    ref = oc.dequant_gemm_fp16_ref(A, packed[cols], "bfloat16", scales[:, cols].contiguous(), 8, 128)
+    _close(C[:, cols.cuda()], ref)
+    C2 = q.w4a16_gemm((Ad * 2), Pd, Sd, 8, 128)
+    torch.testing.assert_close(C2.float(), C.float() * 2, rtol=1e-2, atol=1e-2)  # exact power-of-two scaling in fp32
+    assert torch.isfinite(C.float()).all()
+
+
+def test_config5_prefill_m512_band():
+    q = _q()
+    A, packed, scales = oc.make_config_inputs("cfg5", M=512)
+    C = q.w4a16_gemm(A.cuda(), packed.cuda(), scales.cuda(), 8, 128)
+    cols = torch.cat([torch.arange(0, 128), torch.arange(20000, 20128)])
+    ref = oc.dequant_gemm_fp16_ref(A, packed[cols], "bfloat16", scales[:, cols].contiguous(), 8, 128)
+    _close(C[:, cols.cuda()], ref)
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 64, 256), (128, 128, 512), (256, 256, 1024)])
+def test_w4a8_signed_exact(M, N, K):
+    """The reference's three W4A8 levels (example_dequant_gemm_w4a8.py:202-208), exact int32."""
+    q = _q()
+    g = torch.Generator().manual_seed(42)
+    A = torch.randint(-8, 8, (M, K), dtype=torch.int8, generator=g)
+    Bi = torch.randint(-8, 8, (N, K), dtype=torch.int8, generator=g)
+    qB = oc.pack_int4_signed(Bi)
+    kernel = q.w4a8_gemm_cv(M, N, K)
+    ws = torch.zeros(N, K, dtype=torch.int8, device="cuda")
+    C = torch.zeros(M, N, dtype=torch.int32, device="cuda")
+    out = kernel(A.cuda(), qB.cuda(), ws, C)
+    assert torch.equal(ws.cpu(), Bi)
+    assert torch.equal(out.cpu(), oc.w4a8_gemm_ref(A, qB))
+
+
+def test_w4a8_golden(golden):
+    q = _q()
+    c = golden.case("w4a8")
+    M, K = c["A"].shape
+    N = c["qB"].shape[0]
+    ws = torch.zeros(N, K, dtype=torch.int8, device="cuda")
+    C = torch.zeros(M, N, dtype=torch.int32, device="cuda")
+    q.w4a8_gemm_cv(M, N, K)(c["A"].cuda(), c["qB"].cuda(), ws, C)
+    assert torch.equal(ws.cpu(), c["conv"])
+    assert torch.equal(C.cpu(), c["C_nm"].t())
+
+
+@pytest.mark.parametrize("M,N,K,odt", [(256, 256, 256, "int32"), (512, 512, 512, "int32"), (512, 512, 512, "float16")])
+def test_int8_mode_unsigned_exact(M, N, K, odt):
+    """dequant_gemm_int8_wrapper ladder (example_dequant_gemm_fine_grained.py:459-469)."""
+    q = _q()
+    g = torch.Generator().manual_seed(0)
+    A = torch.randint(-128, 127, (M, K), dtype=torch.int8, generator=g)
+    packed = torch.randint(0, 255, (N, K // 2), dtype=torch.uint8, generator=g)
+    C = q.dequant_gemm_int8_wrapper(M, N, K, 128, 128, 64, odt)(A, packed)
+    ref = oc.dequant_gemm_int8_ref(A, packed, odt)
+    if odt == "int32":
+        assert torch.equal(C, ref)
+    else:
+        torch.testing.assert_close(C, ref, rtol=1e-2, atol=1e-2)
+
+
+def test_unpack_kernel_matches_oracle_on_ragged_sizes():
+    q = _q()
+    g = torch.Generator().manual_seed(1)
+    for N, K in [(1, 2), (3, 34), (17, 96), (64, 1000)]:
+        packed = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)
+        assert torch.equal(q.unpack_int4(packed.cuda()).cpu(), oc.unpack_uint4(packed).to(torch.int8))
+        assert torch.equal(q.unpack_int4(packed.cuda(), signed=True).cpu(), oc.unpack_int4_signed(packed))
+
+
+def test_rejects_bad_arguments():
+    q = _q()
+    A = torch.zeros(4, 64, dtype=torch.float16, device="cuda")
+    P = torch.zeros(16, 32, dtype=torch.uint8, device="cuda")
+    with pytest.raises(ValueError, match="dtype mismatch"):
+        q.w4a16_gemm(A.float(), P)
+    with pytest.raises(ValueError, match="shape mismatch"):
+        q.w4a16_gemm(A, P[:, :16].contiguous())
+    with pytest.raises(q.QGemmError, match="multiple of 32"):
+        q.w4a16_gemm(A[:, :48].contiguous(), P[:, :24].contiguous())
+    with pytest.raises(q.QGemmError, match="group"):
+        q.w4a16_gemm(A, P, torch.ones(4, 16, dtype=torch.float16, device="cuda"), 8, 16)
+    assert torch.equal(q.w4a16_gemm(A, P).cpu(), torch.zeros(4, 16, dtype=torch.float16))

@@ -1,0 +1,396 @@
+// Host side of libqgemm.so: argument validation, TMA tensor-map encoding, kernel selection and launch.
+// The exported functions are declared and documented in include/qgemm.h.
+#include "../../include/qgemm.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "w4a16.cuh"
+#include "w8a8.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+unsigned long long g_wait_limit_ns = 2000ull * 1000ull * 1000ull;
+
+int fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return -1;
+}
+
+#define CUDA_OK(expr)                                                                      \
+  do {                                                                                     \
+    cudaError_t e_ = (expr);                                                               \
+    if (e_ != cudaSuccess) return fail("%s failed: %s", #expr, cudaGetErrorString(e_));   \
+  } while (0)
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+};
+std::mutex g_mu;
+DeviceState g_dev[kMaxDevices];
+EncodeTiledFn g_encode = nullptr;
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+  CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return 0;
+}
+
+template <int BN>
+int set_smem_w8() {
+  using C = qg::W8Cfg<BN>;
+  if (set_smem(qg::w8a8_gemm_kernel<BN, false, false>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w8a8_gemm_kernel<BN, false, true>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w8a8_gemm_kernel<BN, true, false>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w8a8_gemm_kernel<BN, true, true>, C::SMEM_BYTES)) return -1;
+  return 0;
+}
+template <int MT>
+int set_smem_w4() {
+  using C = qg::W4Cfg<MT>;
+  if (set_smem(qg::w4a16_gemm_kernel<MT, false>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_gemm_kernel<MT, true>, C::SMEM_BYTES)) return -1;
+  return 0;
+}
+
+// Once per device, with that device current.
+int ensure_device(int* sm_count) {
+  int dev = 0;
+  CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail("device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState& st = g_dev[dev];
+  if (!st.ready) {
+    cudaDeviceProp prop;
+    CUDA_OK(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10) return fail("libqgemm needs an sm_100a device (B200); device %d is sm_%d%d", dev, prop.major, prop.minor);
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return fail("cuTensorMapEncodeTiled not available from the driver");
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    if (set_smem_w8<128>() || set_smem_w8<256>()) return -1;
+    if (set_smem_w4<16>() || set_smem_w4<32>() || set_smem_w4<64>() || set_smem_w4<128>()) return -1;
+    st.sm_count = prop.multiProcessorCount;
+    st.ready = true;
+  }
+  *sm_count = st.sm_count;
+  return 0;
+}
+
+// rank-2/3 row-major tensor map; dims/box innermost first; strides in bytes for dims 1.. (innermost is dense).
+int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
+               const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz) {
+  cuuint64_t gdim[3], gstr[2];
+  cuuint32_t bx[3], es[3];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i > 0) gstr[i - 1] = strides_bytes[i - 1];
+  }
+  CUresult r = g_encode(map, dt, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return 0;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int BN, bool NK, bool BF>
+int launch_w8(const CUtensorMap& tmA, const CUtensorMap& tmB, const qg::W8A8Params& p, int grid, cudaStream_t s) {
+  qg::w8a8_gemm_kernel<BN, NK, BF><<<grid, qg::W8_THREADS, qg::W8Cfg<BN>::SMEM_BYTES, s>>>(tmA, tmB, p);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+template <int MT>
+int launch_w4(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
+              const qg::W4A16Params& p, int grid, cudaStream_t s) {
+  if (bf)
+    qg::w4a16_gemm_kernel<MT, true><<<grid, qg::W4_THREADS, qg::W4Cfg<MT>::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
+  else
+    qg::w4a16_gemm_kernel<MT, false><<<grid, qg::W4_THREADS, qg::W4Cfg<MT>::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int w4_pick_mt(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+
+constexpr int64_t kW4MaxGrid = 1024;
+constexpr int64_t kW4CounterBytes = kW4MaxGrid * 4;
+
+__global__ void unpack_int4_kernel(const uint8_t* __restrict__ packed, int8_t* __restrict__ out, long long n_bytes,
+                                   int signed_nibbles) {
+  // 16 packed bytes -> 32 int8 values per thread; low nibble first.
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long base = i * 16;
+  if (base >= n_bytes) return;
+  if (base + 16 <= n_bytes) {
+    const uint4 v = *reinterpret_cast<const uint4*>(packed + base);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t lo = w[j] & 0x0f0f0f0fu;         // even elements
+      uint32_t hi = (w[j] >> 4) & 0x0f0f0f0fu;  // odd elements
+      if (signed_nibbles) {                     // two's complement nibble: (x ^ 8) - 8 per byte
+        lo = __vsub4(lo ^ 0x08080808u, 0x08080808u);
+        hi = __vsub4(hi ^ 0x08080808u, 0x08080808u);
+      }
+      o[2 * j] = __byte_perm(lo, hi, 0x5140);      // e0 o0 e1 o1
+      o[2 * j + 1] = __byte_perm(lo, hi, 0x7362);  // e2 o2 e3 o3
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + base * 2);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  } else {
+    for (long long b = base; b < n_bytes; ++b) {
+      int lo = packed[b] & 0xF, hi = packed[b] >> 4;
+      if (signed_nibbles) {
+        lo = (lo ^ 8) - 8;
+        hi = (hi ^ 8) - 8;
+      }
+      out[2 * b] = (int8_t)lo;
+      out[2 * b + 1] = (int8_t)hi;
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int qgemm_version(void) { return 1000; }
+
+const char* qgemm_last_error(void) { return g_err; }
+
+void qgemm_set_wait_limit_ms(uint32_t ms) { g_wait_limit_ns = (unsigned long long)ms * 1000000ull; }
+
+int qgemm_init(void) {
+  int sms = 0;
+  return ensure_device(&sms);
+}
+
+int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const float* scale_a, void* C,
+               int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t scale_b_len,
+               int64_t scale_a_len, int out_dtype, int b_layout, uint32_t* status, void* stream) {
+  if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return fail("qgemm_w8a8: batch, M, N, K must be positive (got %lld, %lld, %lld, %lld)", (long long)batch, (long long)M, (long long)N, (long long)K);
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30) || batch > 65535) return fail("qgemm_w8a8: dimension too large");
+  if (A == nullptr || B == nullptr) return fail("qgemm_w8a8: A and B must not be null");
+  if (b_layout != QGEMM_B_KN && b_layout != QGEMM_B_NK) return fail("qgemm_w8a8: unknown b_layout %d", b_layout);
+  if (out_dtype == QGEMM_DT_I32) {
+    if (C == nullptr) return fail("qgemm_w8a8: int32 output needs C");
+    if (acc_out != nullptr) return fail("qgemm_w8a8: with int32 output pass the buffer as C and acc_out = NULL");
+    acc_out = static_cast<int32_t*>(C);
+    C = nullptr;
+  } else if (out_dtype == QGEMM_DT_F16 || out_dtype == QGEMM_DT_BF16) {
+    if (C == nullptr && acc_out == nullptr) return fail("qgemm_w8a8: neither C nor acc_out given");
+    if (C != nullptr) {
+      if (scale_b == nullptr) return fail("qgemm_w8a8: scale_b must not be null");
+      if (scale_b_len != 1 && scale_b_len != N && scale_b_len != batch * N) return fail("qgemm_w8a8: scale_b_len must be 1, N or batch*N (got %lld)", (long long)scale_b_len);
+      if (scale_a != nullptr && scale_a_len != M && scale_a_len != batch * M) return fail("qgemm_w8a8: scale_a_len must be M or batch*M (got %lld)", (long long)scale_a_len);
+    }
+  } else {
+    return fail("qgemm_w8a8: out_dtype must be F16, BF16 or I32 (got %d)", out_dtype);
+  }
+  if (K % 16 != 0 || N % 16 != 0) return fail("qgemm_w8a8: K and N must be multiples of 16 (got K=%lld, N=%lld)", (long long)K, (long long)N);
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C) || !aligned16(acc_out)) return fail("qgemm_w8a8: A, B, C and acc_out must be 16-byte aligned");
+
+  int sms = 0;
+  if (ensure_device(&sms)) return -1;
+
+  CUtensorMap tmA, tmB;
+  {
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)K, (uint64_t)M * (uint64_t)K};
+    const uint32_t box[3] = {128, 128, 1};
+    if (encode_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, A, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  }
+  const int64_t tiles256 = batch * ((M + 127) / 128) * ((N + 255) / 256);
+  const int BN = (N > 128 && tiles256 >= sms) ? 256 : 128;
+  if (b_layout == QGEMM_B_KN) {
+    const uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)N, (uint64_t)K * (uint64_t)N};
+    const uint32_t box[3] = {128, 128, 1};
+    if (encode_map(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  } else {
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)K, (uint64_t)N * (uint64_t)K};
+    const uint32_t box[3] = {128, (uint32_t)BN, 1};
+    if (encode_map(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  }
+
+  qg::W8A8Params p;
+  p.scale_b = scale_b;
+  p.scale_a = scale_a;
+  p.C = C;
+  p.acc_out = acc_out;
+  p.batch = (int)batch;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.sb_mode = (scale_b_len == 1) ? 0 : ((scale_b_len == N) ? 1 : 2);
+  p.sa_mode = (scale_a == nullptr) ? 0 : ((scale_a_len == M) ? 1 : 2);
+  p.m_tiles = (int)((M + 127) / 128);
+  p.n_tiles = (int)((N + BN - 1) / BN);
+  const int64_t num_tiles = batch * p.m_tiles * p.n_tiles;
+  if (num_tiles > 0x7fffffff) return fail("qgemm_w8a8: too many tiles");
+  p.num_tiles = (int)num_tiles;
+  p.k_blocks = (int)((K + 127) / 128);
+  p.status = status;
+  p.wait_limit_ns = g_wait_limit_ns;
+  p.dbg_lbo = p.dbg_sbo = 0;
+  if (const char* e = getenv("QGEMM_DBG_BDESC")) sscanf(e, "%u,%u", &p.dbg_lbo, &p.dbg_sbo);
+  const int grid = (int)(num_tiles < sms ? num_tiles : sms);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool nk = b_layout == QGEMM_B_NK;
+  const bool bf = out_dtype == QGEMM_DT_BF16;
+  if (BN == 256) {
+    if (nk) return bf ? launch_w8<256, true, true>(tmA, tmB, p, grid, s) : launch_w8<256, true, false>(tmA, tmB, p, grid, s);
+    return bf ? launch_w8<256, false, true>(tmA, tmB, p, grid, s) : launch_w8<256, false, false>(tmA, tmB, p, grid, s);
+  }
+  if (nk) return bf ? launch_w8<128, true, true>(tmA, tmB, p, grid, s) : launch_w8<128, true, false>(tmA, tmB, p, grid, s);
+  return bf ? launch_w8<128, false, true>(tmA, tmB, p, grid, s) : launch_w8<128, false, false>(tmA, tmB, p, grid, s);
+}
+
+int64_t qgemm_w4a16_counter_bytes(void) { return kW4CounterBytes; }
+
+int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  (void)N;
+  (void)K;
+  int sms = 0;
+  if (ensure_device(&sms)) return -1;
+  const int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
+  const int mt = w4_pick_mt(M);
+  // the arrival counters first (fixed place whatever the tile height), then two partial slots of
+  // [MT][128] fp32 per CTA
+  return kW4CounterBytes + grid * 2 * (int64_t)mt * 128 * 4;
+}
+
+int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
+                void* workspace, int64_t workspace_bytes, int64_t M, int64_t N, int64_t K, int a_dtype,
+                int out_dtype, uint32_t* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail("qgemm_w4a16: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M, (long long)N, (long long)K);
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return fail("qgemm_w4a16: dimension too large");
+  if (A == nullptr || B_packed == nullptr || C == nullptr) return fail("qgemm_w4a16: A, B_packed and C must not be null");
+  if (a_dtype != QGEMM_DT_F16 && a_dtype != QGEMM_DT_BF16) return fail("qgemm_w4a16: a_dtype must be F16 or BF16 (got %d)", a_dtype);
+  if (out_dtype != QGEMM_DT_F16 && out_dtype != QGEMM_DT_BF16) return fail("qgemm_w4a16: out_dtype must be F16 or BF16 (got %d)", out_dtype);
+  if (K % 32 != 0) return fail("qgemm_w4a16: K must be a multiple of 32 (got %lld)", (long long)K);
+  if (N % 8 != 0) return fail("qgemm_w4a16: N must be a multiple of 8 (got %lld)", (long long)N);
+  if (!aligned16(A) || !aligned16(B_packed) || !aligned16(C) || !aligned16(scales) || !aligned16(workspace)) return fail("qgemm_w4a16: pointers must be 16-byte aligned");
+  if (scales != nullptr) {
+    if (zero < 0 || zero > 15) return fail("qgemm_w4a16: zero must be in 0..15 (got %d)", zero);
+    if (group <= 0 || K % group != 0) return fail("qgemm_w4a16: group must divide K (got group=%lld, K=%lld)", (long long)group, (long long)K);
+    const bool ok = (group < 256 && 256 % group == 0 && group >= 32) || (group % 256 == 0) || (group >= K);
+    if (!ok) return fail("qgemm_w4a16: group must be 32, 64, 128, a multiple of 256, or the whole K (got %lld)", (long long)group);
+  } else {
+    zero = 0;
+    group = K;
+  }
+  const int64_t need = qgemm_w4a16_workspace_bytes(M, N, K);
+  if (need < 0) return -1;
+  if (workspace == nullptr || workspace_bytes < need) return fail("qgemm_w4a16: workspace of %lld bytes needed (got %lld)", (long long)need, (long long)workspace_bytes);
+
+  int sms = 0;
+  if (ensure_device(&sms)) return -1;
+  const int mt = w4_pick_mt(M);
+
+  CUtensorMap tmW, tmS, tmA;
+  memset(&tmS, 0, sizeof(tmS));
+  {
+    const uint64_t dims[2] = {(uint64_t)(K / 2), (uint64_t)N};
+    const uint64_t str[1] = {(uint64_t)(K / 2)};
+    const uint32_t box[2] = {128, 128};
+    if (encode_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B_packed, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  }
+  int scale_rows = 1;
+  if (scales != nullptr) {
+    scale_rows = group < 256 ? (int)(256 / group) : 1;
+    const uint64_t dims[2] = {(uint64_t)N, (uint64_t)(K / group)};
+    const uint64_t str[1] = {(uint64_t)N * 2};
+    const uint32_t box[2] = {128, (uint32_t)scale_rows};
+    if (encode_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t str[1] = {(uint64_t)K * 2};
+    const uint32_t box[2] = {64, (uint32_t)mt};
+    if (encode_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, A, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  }
+
+  qg::W4A16Params p;
+  p.C = C;
+  p.ws_counters = static_cast<uint32_t*>(workspace);
+  p.ws_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kW4CounterBytes);
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.group = (int)(group > (1 << 30) ? (1 << 30) : group);
+  p.zero = zero;
+  p.has_scales = scales != nullptr;
+  p.a_is_bf16 = a_dtype == QGEMM_DT_BF16;
+  p.m_tiles = (int)((M + mt - 1) / mt);
+  p.n_tiles = (int)((N + 127) / 128);
+  const int64_t num_tiles = (int64_t)p.m_tiles * p.n_tiles;
+  if (num_tiles > 0x3fffffff) return fail("qgemm_w4a16: too many tiles");
+  p.num_tiles = (int)num_tiles;
+  p.KS = (int)((K + 255) / 256);
+  p.scale_rows = scale_rows;
+  p.total_items = num_tiles * p.KS;
+  p.status = status;
+  p.wait_limit_ns = g_wait_limit_ns;
+  int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
+  if (p.total_items < grid) grid = p.total_items;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool bf = out_dtype == QGEMM_DT_BF16;
+  switch (mt) {
+    case 16: return launch_w4<16>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    case 32: return launch_w4<32>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    case 64: return launch_w4<64>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    default: return launch_w4<128>(bf, tmW, tmS, tmA, p, (int)grid, s);
+  }
+}
+
+int qgemm_unpack_int4(const uint8_t* B_packed, int8_t* out, int64_t N, int64_t K, int signed_nibbles,
+                      void* stream) {
+  if (N <= 0 || K <= 0 || (K % 2) != 0) return fail("qgemm_unpack_int4: N, K must be positive and K even (got %lld, %lld)", (long long)N, (long long)K);
+  if (B_packed == nullptr || out == nullptr) return fail("qgemm_unpack_int4: null pointer");
+  if (!aligned16(B_packed) || !aligned16(out)) return fail("qgemm_unpack_int4: pointers must be 16-byte aligned");
+  const long long n_bytes = (long long)N * (K / 2);
+  const long long threads = (n_bytes + 15) / 16;
+  const int block = 256;
+  const long long grid = (threads + block - 1) / block;
+  if (grid > 0x7fffffffll) return fail("qgemm_unpack_int4: tensor too large");
+  unpack_int4_kernel<<<(unsigned)grid, block, 0, static_cast<cudaStream_t>(stream)>>>(B_packed, out, n_bytes, signed_nibbles);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int qgemm_w4a8(const int8_t* A, const uint8_t* qB, int8_t* workspace, void* C, int64_t M, int64_t N, int64_t K,
+               int signed_nibbles, int out_dtype, uint32_t* status, void* stream) {
+  if (workspace == nullptr) return fail("qgemm_w4a8: the int8 [N, K] workspace must not be null");
+  if (K % 32 != 0 || N % 16 != 0) return fail("qgemm_w4a8: K must be a multiple of 32 and N of 16 (got K=%lld, N=%lld)", (long long)K, (long long)N);
+  if (qgemm_unpack_int4(qB, workspace, N, K, signed_nibbles, stream)) return -1;
+  if (out_dtype == QGEMM_DT_I32)
+    return qgemm_w8a8(A, workspace, nullptr, nullptr, C, nullptr, 1, M, N, K, 1, 0, QGEMM_DT_I32, QGEMM_B_NK, status, stream);
+  return fail("qgemm_w4a8: out_dtype must be I32; cast the result on the caller's side (got %d)", out_dtype);
+}
+
+}  // extern "C"

@@ -1,0 +1,476 @@
+// W4A16 dequantize-GEMM for sm_100a:
+//   C[m, n] = cast( sum_k float(A[m, k]) * float(W[n, k]) ),  W[n, k] = half(q[n, k] - zero) * s[k / g, n]
+// with q packed two per byte along K, low nibble first, in B_packed[N, K/2].
+//
+// The weight rows are the MMA "M" dimension (128 per tile, one TMEM lane per weight row) and the
+// tokens are the MMA "N" dimension (MT = 16..128 per tile), so the memory-bound decode shapes stream
+// the packed weights once at full tile height whatever the token count is.
+//
+// Persistent stream-K kernel: the (tile, 256-wide K slab) items are split evenly over the CTAs; a CTA
+// whose slab range covers only part of a tile writes an fp32 partial into scratch memory, and the last
+// contributor of that tile (found with a counter, never by waiting) adds the partials in a fixed order,
+// so results do not depend on arrival order.
+//   warp 0       TMA: packed weights [128 rows x 128 B] + the slab's scales into the "raw" ring
+//   warp 1       tcgen05.mma kind::f16 issuer, fp32 accumulators in tensor memory (double buffered)
+//   warp 2       TMA: activation tiles straight into the operand ring
+//   warps 3..6   epilogue (TMEM -> registers -> global / scratch, split-K reduction)
+//   warps 7..14  dequant: 16 B of nibbles -> lop3 magic-number conversion -> (q - zero) * s in f16x2 ->
+//                swizzled K-major operand tile in shared memory; the same warps permute (and, for
+//                bf16 input, convert) the activation tile in place so both operands share one K order.
+#pragma once
+
+#include "common.cuh"
+
+namespace qg {
+
+struct W4A16Params {
+  void* C;               // [M, N] f16 / bf16
+  float* ws_partials;    // scratch: 2 * grid slots of [MT][128] fp32
+  uint32_t* ws_counters; // scratch: grid counters, zero on entry, left zero on exit
+  int M, N, K;
+  int group;            // quantisation group size along K
+  int zero;             // integer zero point (0..15)
+  int has_scales;       // 0: weights are the raw nibble values (scale 1)
+  int a_is_bf16;        // activations are bf16 (converted to f16 in shared memory) instead of f16
+  int m_tiles, n_tiles, num_tiles;
+  int KS;               // 256-wide K slabs per tile
+  int scale_rows;       // scale rows fetched per slab (256 / group, at least 1)
+  long long total_items;
+  uint32_t* status;
+  unsigned long long wait_limit_ns;
+};
+
+constexpr int W4_BN = 128;        // weight rows per tile
+constexpr int W4_SLAB_K = 256;    // K per raw stage: 128 packed bytes per row
+constexpr int W4_HALF_K = 128;    // K per operand stage: two 64-wide swizzle atoms of f16
+constexpr int W4_THREADS = 480;
+constexpr int W4_DQ_WARPS = 8;
+constexpr int W4_RAW_PACKED = W4_BN * 128;         // 16 KB
+constexpr int W4_RAW_BYTES = W4_RAW_PACKED + 2048; // + up to 8 scale rows of 128 halves
+
+template <int MT>
+struct W4Cfg {
+  static constexpr int RAW_STAGES = (MT <= 64) ? 4 : 3;
+  static constexpr int DEQ_STAGES = (MT <= 64) ? 3 : 2;
+  static constexpr int W_KB_BYTES = W4_BN * 128;  // one 64-wide K block of f16 weights: 16 KB
+  static constexpr int A_KB_BYTES = MT * 128;     // one 64-wide K block of activations
+  static constexpr int DEQ_BYTES = 2 * W_KB_BYTES + 2 * A_KB_BYTES;
+  static constexpr int TMEM_COLS = (2 * MT < 32) ? 32 : 2 * MT;
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int SMEM_BYTES = RAW_STAGES * W4_RAW_BYTES + DEQ_STAGES * DEQ_BYTES + BAR_BYTES + 1024;
+  static constexpr int CH = (MT < 32) ? 16 : 32;  // accumulator columns per TMEM load
+};
+
+// Contiguous item range of CTA `b` out of `G`: [T*b/G, T*(b+1)/G).
+__device__ __forceinline__ long long w4_range_begin(long long T, int G, int b) { return T * b / G; }
+// The CTA whose range holds item i.
+__device__ __forceinline__ int w4_owner(long long T, int G, long long i) { return (int)(((i + 1) * G - 1) / T); }
+
+struct W4SegIter {
+  long long item, end;
+  int KS;
+  __device__ __forceinline__ bool next(int& tile, int& ks0, int& ks1) {
+    if (item >= end) return false;
+    tile = (int)(item / KS);
+    ks0 = (int)(item - (long long)tile * KS);
+    const long long rem = end - item;
+    ks1 = (rem < (long long)(KS - ks0)) ? (int)(ks0 + rem) : KS;
+    item += ks1 - ks0;
+    return true;
+  }
+};
+
+// Eight packed nibbles n0..n7 (n_j at bits 4j) -> eight f16 values (n_j - zero) [* s], emitted as the
+// half2 words (n0,n4) (n1,n5) (n2,n6) (n3,n7): the cheapest order for the magic-number conversion.
+// Low nibbles: 0x6400 | n = 1024 + n, minus (1024 + zero).  High nibbles: 0x6400 | (n << 4) = 1024 + 16 n,
+// times 1/16 minus (64 + zero).  Both are exact; the product with s rounds once (RN), like an f16 multiply.
+__device__ __forceinline__ uint4 w4_dequant8(uint32_t x, uint32_t sub_lo, uint32_t sub_hi, uint32_t s2, bool scaled) {
+  uint32_t lo0, hi0, lo1, hi1;
+  const uint32_t y = x >> 8;
+  asm volatile("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(lo0) : "r"(x));
+  asm volatile("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hi0) : "r"(x));
+  asm volatile("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(lo1) : "r"(y));
+  asm volatile("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hi1) : "r"(y));
+  const uint32_t sixteenth = 0x2C002C00u;  // 1/16
+  uint4 o;
+  asm volatile("sub.rn.f16x2 %0, %1, %2;" : "=r"(o.x) : "r"(lo0), "r"(sub_lo));
+  asm volatile("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(o.y) : "r"(hi0), "r"(sixteenth), "r"(sub_hi));
+  asm volatile("sub.rn.f16x2 %0, %1, %2;" : "=r"(o.z) : "r"(lo1), "r"(sub_lo));
+  asm volatile("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(o.w) : "r"(hi1), "r"(sixteenth), "r"(sub_hi));
+  if (scaled) {
+    asm volatile("mul.rn.f16x2 %0, %0, %1;" : "+r"(o.x) : "r"(s2));
+    asm volatile("mul.rn.f16x2 %0, %0, %1;" : "+r"(o.y) : "r"(s2));
+    asm volatile("mul.rn.f16x2 %0, %0, %1;" : "+r"(o.z) : "r"(s2));
+    asm volatile("mul.rn.f16x2 %0, %0, %1;" : "+r"(o.w) : "r"(s2));
+  }
+  return o;
+}
+
+__device__ __forceinline__ uint32_t w4_bf16x2_to_f16x2(uint32_t w) {
+  const float lo = __uint_as_float(w << 16);
+  const float hi = __uint_as_float(w & 0xffff0000u);
+  return pack_f16x2(lo, hi);
+}
+
+// Eight consecutive K elements (a0..a7, as four 32-bit words) -> the words (a0,a4) (a1,a5) (a2,a6) (a3,a7).
+__device__ __forceinline__ uint4 w4_permute_act(uint4 v) {
+  uint4 o;
+  o.x = __byte_perm(v.x, v.z, 0x5410);
+  o.y = __byte_perm(v.x, v.z, 0x7632);
+  o.z = __byte_perm(v.y, v.w, 0x5410);
+  o.w = __byte_perm(v.y, v.w, 0x7632);
+  return o;
+}
+
+__device__ __forceinline__ void w4_epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int MT, bool OUT_BF16>
+__global__ void __launch_bounds__(W4_THREADS, 1)
+w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
+                  const __grid_constant__ CUtensorMap tmA, const W4A16Params p) {
+  using Cfg = W4Cfg<MT>;
+  constexpr int RS = Cfg::RAW_STAGES;
+  constexpr int DS = Cfg::DEQ_STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* raw_base = smem;
+  uint8_t* deq_base = smem + RS * W4_RAW_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(deq_base + DS * Cfg::DEQ_BYTES);
+  uint64_t* raw_full = bars;
+  uint64_t* raw_empty = raw_full + RS;
+  uint64_t* a_full = raw_empty + RS;
+  uint64_t* deq_full = a_full + DS;
+  uint64_t* deq_empty = deq_full + DS;
+  uint64_t* tfull = deq_empty + DS;
+  uint64_t* tempty = tfull + 2;
+  uint64_t* drain = tempty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* epi_flag = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < RS; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], W4_DQ_WARPS);
+    }
+    for (int s = 0; s < DS; ++s) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&deq_full[s], W4_DQ_WARPS);
+      mbar_init(&deq_empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    *epi_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmA);
+    if (p.has_scales) tma_prefetch_desc(&tmS);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns};
+
+  const int G = gridDim.x;
+  const int cta = blockIdx.x;
+  const long long T = p.total_items;
+  W4SegIter seg{w4_range_begin(T, G, cta), w4_range_begin(T, G, cta + 1), p.KS};
+  int tile, ks0, ks1;
+
+  if (warp == 0) {
+    // ------------------------------------------- raw producer: packed weights + scales
+    if (lane == 0) {
+      int rs = 0;
+      uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
+      bool ok = true;
+      const uint32_t tx = W4_RAW_PACKED + (p.has_scales ? p.scale_rows * 256 : 0);
+      while (ok && seg.next(tile, ks0, ks1)) {
+        const int n0 = (tile / p.m_tiles) * W4_BN;
+        for (int ks = ks0; ks < ks1; ++ks) {
+          if (!mbar_wait(&raw_empty[rs], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* dst = raw_base + rs * W4_RAW_BYTES;
+          mbar_arrive_expect_tx(&raw_full[rs], tx);
+          tma_load_2d(dst, &tmW, &raw_full[rs], ks * (W4_SLAB_K / 2), n0);
+          if (p.has_scales) {
+            const int srow = (p.group <= W4_SLAB_K) ? ks * p.scale_rows : (ks * W4_SLAB_K) / p.group;
+            tma_load_2d(dst + W4_RAW_PACKED, &tmS, &raw_full[rs], n0, srow);
+          }
+          issued_mask |= 1u << rs;
+          parity_mask = (parity_mask & ~(1u << rs)) | (phase << rs);
+          if (++rs == RS) { rs = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        for (int s = 0; s < RS; ++s) {
+          if (!(issued_mask & (1u << s))) continue;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(&raw_full[s], (parity_mask >> s) & 1u)) {
+            if (global_timer_ns() - t0 > p.wait_limit_ns) {
+              if (p.status) atomicMax(p.status, (uint32_t)ST_TIMEOUT_DRAIN);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------- activation producer
+    if (lane == 0) {
+      int ds = 0;
+      uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
+      bool ok = true;
+      while (ok && seg.next(tile, ks0, ks1)) {
+        const int m0 = (tile % p.m_tiles) * MT;
+        for (int ks = ks0; ok && ks < ks1; ++ks) {
+          for (int h = 0; h < 2; ++h) {
+            if (!mbar_wait(&deq_empty[ds], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+            uint8_t* dstA = deq_base + ds * Cfg::DEQ_BYTES + 2 * Cfg::W_KB_BYTES;
+            mbar_arrive_expect_tx(&a_full[ds], 2 * Cfg::A_KB_BYTES);
+            const int k0 = ks * W4_SLAB_K + h * W4_HALF_K;
+            tma_load_2d(dstA, &tmA, &a_full[ds], k0, m0);
+            tma_load_2d(dstA + Cfg::A_KB_BYTES, &tmA, &a_full[ds], k0 + 64, m0);
+            issued_mask |= 1u << ds;
+            parity_mask = (parity_mask & ~(1u << ds)) | (phase << ds);
+            if (++ds == DS) { ds = 0; phase ^= 1u; }
+          }
+        }
+      }
+      if (!ok) {
+        for (int s = 0; s < DS; ++s) {
+          if (!(issued_mask & (1u << s))) continue;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(&a_full[s], (parity_mask >> s) & 1u)) {
+            if (global_timer_ns() - t0 > p.wait_limit_ns) {
+              if (p.status) atomicMax(p.status, (uint32_t)ST_TIMEOUT_DRAIN);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(ACC_F32, FMT_F16, FMT_F16, 0, 0, W4_BN, MT);
+      int ds = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      while (ok && seg.next(tile, ks0, ks1)) {
+        const int buf = it & 1;
+        const uint32_t tphase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d = tmem_base + buf * MT;
+        uint32_t acc = 0;
+        for (int i = 0; ok && i < 2 * (ks1 - ks0); ++i) {
+          if (!mbar_wait(&deq_full[ds], phase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sW = smem_u32(deq_base + ds * Cfg::DEQ_BYTES);
+          const uint32_t sA = sW + 2 * Cfg::W_KB_BYTES;
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb) {
+            const uint64_t wd = make_desc_kmajor(sW + kb * Cfg::W_KB_BYTES);
+            const uint64_t ad = make_desc_kmajor(sA + kb * Cfg::A_KB_BYTES);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {  // 16 f16 = 32 bytes per MMA
+              umma_f16_ss(d, wd + (uint64_t)(2 * k), ad + (uint64_t)(2 * k), idesc, acc);
+              acc = 1;
+            }
+          }
+          umma_commit(&deq_empty[ds]);
+          if (++ds == DS) { ds = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&tfull[buf]);
+        ++it;
+      }
+      if (!ok) {
+        umma_commit(drain);
+        const uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(drain, 0)) {
+          if (global_timer_ns() - t0 > p.wait_limit_ns) break;
+        }
+      }
+    }
+  } else if (warp >= 3 && warp < 7) {
+    // ---------------------------------------------------------------- epilogue
+    constexpr int CH = Cfg::CH;
+    const int q = warp & 3;
+    const int nl = q * 32 + lane;  // weight row inside the tile == TMEM lane
+    uint16_t* Cout = reinterpret_cast<uint16_t*>(p.C);
+    int it = 0;
+    while (seg.next(tile, ks0, ks1)) {
+      const int buf = it & 1;
+      const uint32_t tphase = (it >> 1) & 1;
+      ++it;
+      const int n = (tile / p.m_tiles) * W4_BN + nl;
+      const int m0 = (tile % p.m_tiles) * MT;
+      const bool full_tile = (ks0 == 0 && ks1 == p.KS);
+      const int my_slot = (ks1 < p.KS) ? 2 * cta + 1 : 2 * cta;
+      const bool ok = mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE);
+      if (ok) {
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * MT;
+#pragma unroll 1
+        for (int c = 0; c < MT / CH; ++c) {
+          uint32_t r[CH];
+          if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + c * CH, r);
+          else tmem_ld_32x32b_x32(taddr + c * CH, r);
+          tmem_ld_wait();
+          if (full_tile) {
+            if (n < p.N) {
+#pragma unroll
+              for (int j = 0; j < CH; ++j) {
+                const int m = m0 + c * CH + j;
+                if (m < p.M) {
+                  const float v = __uint_as_float(r[j]);
+                  Cout[(size_t)m * p.N + n] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
+                                                       : __half_as_ushort(__float2half_rn(v));
+                }
+              }
+            }
+          } else {
+            float* dst = p.ws_partials + (size_t)my_slot * (MT * W4_BN) + (size_t)(c * CH) * W4_BN + nl;
+#pragma unroll
+            for (int j = 0; j < CH; ++j) dst[j * W4_BN] = __uint_as_float(r[j]);
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[buf]);
+      }
+      if (full_tile) {
+        if (!ok) break;
+        continue;
+      }
+      // Split tile: publish the partial, count arrivals; the last contributor reduces in a fixed order.
+      const long long first_item = (long long)tile * p.KS;
+      const int b_first = w4_owner(T, G, first_item);
+      const int b_last = w4_owner(T, G, first_item + p.KS - 1);
+      __threadfence();
+      w4_epi_bar();
+      if (warp == 3 && lane == 0) {
+        uint32_t last = 0;
+        if (!*abort_flag) {
+          const uint32_t old = atomicAdd(p.ws_counters + b_first, 1u);
+          if (old == (uint32_t)(b_last - b_first)) {
+            last = 1;
+            p.ws_counters[b_first] = 0;  // every contributor has arrived: leave the counter clean
+          }
+        }
+        *epi_flag = last;
+      }
+      w4_epi_bar();
+      const bool is_last = *epi_flag != 0;
+      const bool aborted = *abort_flag != 0;
+      w4_epi_bar();  // epi_flag may be rewritten only after everyone has read it
+      if (aborted) break;
+      if (is_last) {
+        __threadfence();
+        if (n < p.N) {
+          for (int m = 0; m < MT && m0 + m < p.M; ++m) {
+            float sum = 0.0f;
+            for (int c = b_first; c <= b_last; ++c) {
+              const long long c_end = w4_range_begin(T, G, c + 1);
+              const bool reaches_end = c_end >= first_item + p.KS;
+              const int slot = reaches_end ? 2 * c : 2 * c + 1;
+              sum += __ldcg(p.ws_partials + (size_t)slot * (MT * W4_BN) + (size_t)m * W4_BN + nl);
+            }
+            Cout[(size_t)(m0 + m) * p.N + n] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum))
+                                                       : __half_as_ushort(__float2half_rn(sum));
+          }
+        }
+      }
+    }
+  } else if (warp >= 7) {
+    // ----------------------------------------------------------------- dequant
+    const int wd = warp - 7;
+    const int tid_d = wd * 32 + lane;
+    const int rr = lane >> 2;
+    const int c4 = lane & 3;
+    const int row_lo = wd * 8 + (((rr & 1) << 2) | (rr >> 1));  // rows r, r+4 share a quarter-warp: no bank conflicts
+    const int sw = row_lo & 7;
+    const uint32_t zero = (uint32_t)p.zero;
+    const uint32_t sub_lo = (0x6400u + zero) * 0x00010001u;                      // (1024 + zero) x2
+    const uint32_t sub_hi = ((0x5400u + (zero << 4)) | 0x8000u) * 0x00010001u;   // -(64 + zero) x2
+    const bool scaled = p.has_scales != 0;
+    int rs = 0, ds = 0;
+    uint32_t rphase = 0, dphase = 0;
+    bool ok = true;
+    while (ok && seg.next(tile, ks0, ks1)) {
+      for (int ks = ks0; ok && ks < ks1; ++ks) {
+        if (!mbar_wait_warp(&raw_full[rs], rphase, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
+        const uint8_t* rawp = raw_base + rs * W4_RAW_BYTES;
+        const __half* sS = reinterpret_cast<const __half*>(rawp + W4_RAW_PACKED);
+        for (int h = 0; h < 2; ++h) {
+          if (!mbar_wait_warp(&deq_empty[ds], dphase ^ 1u, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
+          uint8_t* dW = deq_base + ds * Cfg::DEQ_BYTES + (c4 >> 1) * Cfg::W_KB_BYTES;
+          const int chunk = 4 * h + c4;          // 16-byte packed chunk of the 128-byte row
+          const int kloc = h * W4_HALF_K + c4 * 32;
+          const int srow = (p.group <= W4_SLAB_K) ? kloc / p.group : 0;
+#pragma unroll
+          for (int pass = 0; pass < 2; ++pass) {
+            const int row = row_lo + pass * 64;
+            const uint4 v = *reinterpret_cast<const uint4*>(rawp + row * 128 + ((chunk ^ sw) << 4));
+            uint32_t s2 = 0x3C003C00u;
+            if (scaled) s2 = (uint32_t)__half_as_ushort(sS[srow * W4_BN + row]) * 0x00010001u;
+            const uint32_t xs[4] = {v.x, v.y, v.z, v.w};
+            uint8_t* drow = dW + row * 128;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 o = w4_dequant8(xs[j], sub_lo, sub_hi, s2, scaled);
+              *reinterpret_cast<uint4*>(drow + (((((c4 & 1) << 2) + j) ^ sw) << 4)) = o;
+            }
+          }
+          // Activations for this stage: permute K inside every group of eight (and convert bf16 -> f16) in place.
+          if (!mbar_wait_warp(&a_full[ds], dphase, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
+          uint4* aT = reinterpret_cast<uint4*>(deq_base + ds * Cfg::DEQ_BYTES + 2 * Cfg::W_KB_BYTES);
+#pragma unroll
+          for (int i = 0; i < (2 * Cfg::A_KB_BYTES / 16 + 255) / 256; ++i) {
+            const int idx = tid_d + i * 256;
+            if (idx < 2 * Cfg::A_KB_BYTES / 16) {
+              uint4 v = aT[idx];
+              if (p.a_is_bf16) {
+                v.x = w4_bf16x2_to_f16x2(v.x);
+                v.y = w4_bf16x2_to_f16x2(v.y);
+                v.z = w4_bf16x2_to_f16x2(v.z);
+                v.w = w4_bf16x2_to_f16x2(v.w);
+              }
+              aT[idx] = w4_permute_act(v);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&deq_full[ds]);
+          if (++ds == DS) { ds = 0; dphase ^= 1u; }
+        }
+        __syncwarp();
+        if (ok && lane == 0) mbar_arrive(&raw_empty[rs]);
+        if (++rs == RS) { rs = 0; rphase ^= 1u; }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace qg

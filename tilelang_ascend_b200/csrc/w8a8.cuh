@@ -1,0 +1,263 @@
+// W8A8 quantized (batched) matmul for sm_100a:
+//   C[b, m, n] = cast( float(sum_k int32(A[b,m,k]) * int32(B[b,k,n])) [* scale_a[m]] * scale_b[n] )
+//
+// Persistent, warp-specialised kernel. One CTA per SM walks a list of 128 x BN output tiles:
+//   warp 0      TMA producer: A tile [128 x 128 B] and B tile into a multistage shared-memory ring
+//   warp 1      tcgen05.mma kind::i8 issuer; int32 accumulators live in tensor memory, double buffered
+//   warps 2..5  epilogue: tcgen05.ld -> cvt.rn.f32.s32 -> fp32 scale(s) -> cvt.rn f16/bf16 -> 16-byte stores
+// B is consumed in the operator's own [K, N] row-major layout as an MN-major operand (no transpose
+// pass), or in [N, K] layout as a K-major operand.
+#pragma once
+
+#include "common.cuh"
+
+namespace qg {
+
+struct W8A8Params {
+  const float* scale_b;
+  const float* scale_a;  // nullable
+  void* C;               // [batch, M, N] f16 / bf16
+  int32_t* acc_out;      // nullable: raw int32 accumulators [batch, M, N]
+  int batch, M, N, K;
+  int sb_mode;  // 0: one value for all; 1: [N]; 2: [batch, N]
+  int sa_mode;  // 0: none; 1: [M]; 2: [batch, M]
+  int m_tiles, n_tiles, num_tiles, k_blocks;
+  uint32_t* status;  // nullable device word
+  unsigned long long wait_limit_ns;
+  uint32_t dbg_lbo, dbg_sbo;  // bring-up only: non-zero overrides of the MN-major B descriptor offsets
+};
+
+constexpr int W8_BM = 128;      // tile rows (= MMA M, one TMEM lane per row)
+constexpr int W8_BK = 128;      // K bytes per pipeline stage (one 128-byte swizzle atom)
+constexpr int W8_UMMA_K = 32;   // K per tcgen05.mma for 8-bit operands
+constexpr int W8_THREADS = 192;
+constexpr int W8_GROUP_M = 8;   // tile rasterisation: walk 8 row-tiles per column-tile band
+
+template <int BN>
+struct W8Cfg {
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int A_BYTES = W8_BM * W8_BK;
+  static constexpr int B_BYTES = BN * W8_BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void w8_decode_tile(const W8A8Params& p, int tile, int& b, int& m_blk, int& n_blk) {
+  const int per_batch = p.m_tiles * p.n_tiles;
+  b = tile / per_batch;
+  const int r = tile - b * per_batch;
+  const int band = W8_GROUP_M * p.n_tiles;
+  const int g = r / band;
+  const int first_m = g * W8_GROUP_M;
+  const int gsz = min(p.m_tiles - first_m, W8_GROUP_M);
+  const int in_band = r - g * band;
+  m_blk = first_m + in_band % gsz;
+  n_blk = in_band / gsz;
+}
+
+template <int BN, bool B_NK, bool OUT_BF16>
+__global__ void __launch_bounds__(W8_THREADS, 1)
+w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const W8A8Params p) {
+  using Cfg = W8Cfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint64_t* drain = tempty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns};
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int b, m_blk, n_blk;
+        w8_decode_tile(p, tile, b, m_blk, n_blk);
+        const int m0 = m_blk * W8_BM, n0 = n_blk * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* sA = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sB = sA + Cfg::A_BYTES;
+          mbar_arrive_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          tma_load_3d(sA, &tmA, &full[stage], kb * W8_BK, m0, b);
+          if constexpr (B_NK) {
+            tma_load_3d(sB, &tmB, &full[stage], kb * W8_BK, n0, b);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 128; ++c)
+              tma_load_3d(sB + c * (W8_BK * 128), &tmB, &full[stage], n0 + c * 128, kb * W8_BK, b);
+          }
+          issued_mask |= 1u << stage;
+          parity_mask = (parity_mask & ~(1u << stage)) | (phase << stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Gave up: wait (bounded) until every bulk copy already issued has landed before the CTA may exit.
+        for (int s = 0; s < STAGES; ++s) {
+          if (!(issued_mask & (1u << s))) continue;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(&full[s], (parity_mask >> s) & 1u)) {
+            if (global_timer_ns() - t0 > p.wait_limit_ns) {
+              if (p.status) atomicMax(p.status, (uint32_t)ST_TIMEOUT_DRAIN);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, B_NK ? 0 : 1, W8_BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t tphase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sA = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sB = sA + Cfg::A_BYTES;
+          const uint64_t a0 = make_desc_kmajor(sA);
+#pragma unroll
+          for (int k = 0; k < W8_BK / W8_UMMA_K; ++k) {
+            const uint64_t adesc = a0 + (uint64_t)((k * W8_UMMA_K) >> 4);
+            uint64_t bdesc;
+            if constexpr (B_NK) {
+              bdesc = make_desc_kmajor(sB) + (uint64_t)((k * W8_UMMA_K) >> 4);
+            } else {
+              // [K rows][128 B of N]: 32 K rows per MMA = 4096 B; the next 128 columns are one box (16 KB) further.
+              bdesc = make_smem_desc_sw128(sB + k * (W8_UMMA_K * 128), p.dbg_lbo ? p.dbg_lbo : W8_BK * 128,
+                                           p.dbg_sbo ? p.dbg_sbo : 1024);
+            }
+            umma_i8_ss(d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&tfull[buf]);
+      }
+      if (!ok) {
+        umma_commit(drain);
+        const uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(drain, 0)) {
+          if (global_timer_ns() - t0 > p.wait_limit_ns) break;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      int b, m_blk, n_blk;
+      w8_decode_tile(p, tile, b, m_blk, n_blk);
+      const int buf = it & 1;
+      const uint32_t tphase = (it >> 1) & 1;
+      if (!mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after_sync();
+      const int m = m_blk * W8_BM + q * 32 + lane;
+      const bool row_ok = m < p.M;
+      float sa = 1.0f;
+      if (p.sa_mode != 0 && row_ok) sa = __ldg(p.scale_a + (p.sa_mode == 2 ? (size_t)b * p.M : 0) + m);
+      const float* sbp = p.scale_b + (p.sb_mode == 2 ? (size_t)b * p.N : 0);
+      const size_t row_off = ((size_t)b * p.M + (row_ok ? m : 0)) * (size_t)p.N;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int n = n_blk * BN + c * 32;
+        if (row_ok && n < p.N) {
+          if (p.acc_out != nullptr) {
+            int4* dst = reinterpret_cast<int4*>(p.acc_out + row_off + n);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (n + 4 * j < p.N) dst[j] = make_int4((int)r[4 * j], (int)r[4 * j + 1], (int)r[4 * j + 2], (int)r[4 * j + 3]);
+          }
+          uint16_t* cbase = reinterpret_cast<uint16_t*>(p.C) + row_off + n;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (p.C != nullptr && n + 8 * j < p.N) {
+              uint32_t o[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int col = 8 * j + 2 * e;
+                float s0, s1;
+                if (p.sb_mode == 0) { s0 = s1 = __ldg(sbp); }
+                else { s0 = __ldg(sbp + n + col); s1 = __ldg(sbp + n + col + 1); }
+                float f0 = __int2float_rn((int)r[col]);
+                float f1 = __int2float_rn((int)r[col + 1]);
+                if (p.sa_mode != 0) { f0 = __fmul_rn(f0, sa); f1 = __fmul_rn(f1, sa); }
+                f0 = __fmul_rn(f0, s0);
+                f1 = __fmul_rn(f1, s1);
+                o[e] = pack_out2<OUT_BF16>(f0, f1);
+              }
+              *reinterpret_cast<uint4*>(cbase + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[buf]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace qg

@@ -1,0 +1,368 @@
+"""Operator factories with the names, argument order and call signatures of the reference examples.
+
+Reference                                                              here
+---------------------------------------------------------------------  -------------------------------
+examples/quant_batch_matmul/example_quant_batch_matmul.py:17-91        simple_quant_batch_matmul
+examples/quant_batch_matmul/example_quant_matmul.py:17-90              simple_quant_matmul
+examples/dequantize_gemm/example_dequant_gemm_fine_grained.py:176-223  dequant_gemm_fp16_wrapper
+examples/dequantize_gemm/example_dequant_gemm_fine_grained.py:226-266  dequant_gemm_int8_wrapper
+examples/dequantize_gemm/example_dequant_gemm_w4a8.py:25-121           w4a8_gemm_cv
+
+As in the reference, a factory is called with the static shape and returns a callable that takes
+torch tensors and returns a torch tensor; outputs and workspaces are allocated by the wrapper on the
+device of the first input (tilelang/jit/adapter/cython/cython_wrapper.pyx:102-141), inputs must be
+contiguous, of the declared dtype and on one device, else ``ValueError`` (:148-180).  The ``block_*``
+arguments are kept for signature parity; the tile sizes of the B200 kernels are fixed by the library.
+Every call goes through the C ABI of libqgemm.so; there is no fallback path.
+"""
+from __future__ import annotations
+
+import functools
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_TORCH_DT = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32,
+             "int8": torch.int8, "int32": torch.int32}
+_ABI_DT = {torch.float16: _lib.DT_F16, torch.bfloat16: _lib.DT_BF16, torch.int32: _lib.DT_I32}
+
+
+def _dt(x):
+    if isinstance(x, torch.dtype):
+        return x
+    try:
+        return _TORCH_DT[x]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {x!r}") from None
+
+
+def _stream_handle(stream, device) -> int:
+    if stream is None or stream == -1:
+        return torch.cuda.current_stream(device).cuda_stream
+    if isinstance(stream, torch.cuda.Stream):
+        return stream.cuda_stream
+    return int(stream)
+
+
+def _check_tensor(t, idx, name, dtype, shape, device):
+    if not isinstance(t, torch.Tensor):
+        raise ValueError(f"Unsupported tensor type: {type(t)}")
+    if not t.is_contiguous():
+        raise ValueError(f"Input tensor at index {idx} must be contiguous")
+    if t.device != device:
+        raise ValueError(f"Buffer device mismatch for parameter {name}: expected {device}, got {t.device}")
+    if t.dtype != dtype:
+        raise ValueError(f"Buffer dtype mismatch for parameter {name}: expected {dtype}, got {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"Static shape mismatch for parameter {name}: expected {tuple(shape)}, got {tuple(t.shape)}")
+
+
+def _require_cuda(t, name):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda):
+        raise ValueError(f"parameter {name} must be a CUDA tensor (this operator has no CPU path)")
+
+
+def _check_blocks(*blocks):
+    for b in blocks:
+        if not isinstance(b, int) or b <= 0:
+            raise ValueError(f"block sizes must be positive integers, got {b!r}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+# ------------------------------------------------------------------------------------------- W8A8
+def quant_matmul(A, B, scale, scale_a=None, out_dtype=torch.float16, b_layout="KN", stream=None,
+                 return_accumulators=False, status=None):
+    """``C = cast((int32(A @ B)).float() [* scale_a[..., None]] * scale)`` on CUDA int8 tensors.
+
+    A: [M, K] or [Batch, M, K]; B: [K, N] / [Batch, K, N] (``b_layout="KN"``) or [N, K] / [Batch, N, K]
+    (``"NK"``).  scale: fp32 [1], [N] or [Batch, N].  scale_a: optional fp32 [M] or [Batch, M].
+    ``out_dtype`` float16 / bfloat16, or int32 for the raw accumulators.
+    """
+    lib = _lib.load()
+    _require_cuda(A, "A")
+    dev = A.device
+    out_dtype = _dt(out_dtype)
+    if A.dim() not in (2, 3) or B.dim() != A.dim():
+        raise ValueError("A and B must both be 2-D or both be 3-D")
+    batched = A.dim() == 3
+    batch = A.shape[0] if batched else 1
+    M, K = A.shape[-2], A.shape[-1]
+    if b_layout == "KN":
+        N = B.shape[-1]
+        b_shape = ((batch,) if batched else ()) + (K, N)
+    elif b_layout == "NK":
+        N = B.shape[-2]
+        b_shape = ((batch,) if batched else ()) + (N, K)
+    else:
+        raise ValueError("b_layout must be 'KN' or 'NK'")
+    _check_tensor(A, 0, "A", torch.int8, None, dev)
+    _check_tensor(B, 1, "B", torch.int8, b_shape, dev)
+    sb_len = sa_len = 0
+    if out_dtype != torch.int32:
+        _check_tensor(scale, 2, "scale", torch.float32, None, dev)
+        sb_len = scale.numel()
+        if sb_len not in (1, N, batch * N):
+            raise ValueError(f"Static shape mismatch for parameter scale: expected [1], [{N}] or [{batch}, {N}], got {tuple(scale.shape)}")
+        if scale_a is not None:
+            _check_tensor(scale_a, 3, "scale_a", torch.float32, None, dev)
+            sa_len = scale_a.numel()
+            if sa_len not in (M, batch * M):
+                raise ValueError(f"Static shape mismatch for parameter scale_a: expected [{M}] or [{batch}, {M}], got {tuple(scale_a.shape)}")
+    elif out_dtype not in _ABI_DT:
+        raise ValueError(f"unsupported out_dtype {out_dtype}")
+    out_shape = ((batch,) if batched else ()) + (M, N)
+    C = torch.empty(out_shape, dtype=out_dtype, device=dev)
+    acc = torch.empty(out_shape, dtype=torch.int32, device=dev) if (return_accumulators and out_dtype != torch.int32) else None
+    with torch.cuda.device(dev):
+        rc = lib.qgemm_w8a8(A.data_ptr(), B.data_ptr(), _ptr(scale) if out_dtype != torch.int32 else None,
+                            _ptr(scale_a) if out_dtype != torch.int32 else None, C.data_ptr(), _ptr(acc),
+                            batch, M, N, K, sb_len, sa_len, _ABI_DT[out_dtype],
+                            _lib.B_KN if b_layout == "KN" else _lib.B_NK, _ptr(status), _stream_handle(stream, dev))
+    _lib.check(rc, "qgemm_w8a8")
+    if acc is not None:
+        return C, acc
+    return C
+
+
+class _QuantMatmulKernel:
+    """Callable returned by the W8A8 factories: ``kernel(A, B, scale[, scale_a]) -> C``."""
+
+    def __init__(self, batch, M, N, K, scale_size, out_dtype):
+        self.batch, self.M, self.N, self.K = batch, M, N, K
+        self.scale_size = scale_size
+        self.out_dtype = out_dtype
+
+    def __call__(self, A, B, scale, scale_a=None, stream=None, return_accumulators=False):
+        lead = () if self.batch is None else (self.batch,)
+        _require_cuda(A, "A")
+        _check_tensor(A, 0, "A", torch.int8, lead + (self.M, self.K), A.device)
+        _check_tensor(B, 1, "B", torch.int8, lead + (self.K, self.N), A.device)
+        if isinstance(scale, torch.Tensor) and scale_a is None:
+            n_scale = self.N if str(self.scale_size) == "N" else 1
+            allowed = {n_scale} | ({self.batch * self.N} if (self.batch and n_scale != 1) else set())
+            if scale.numel() not in allowed:
+                raise ValueError(f"Static shape mismatch for parameter scale: expected [{n_scale}], got {tuple(scale.shape)}")
+        return quant_matmul(A, B, scale, scale_a=scale_a, out_dtype=self.out_dtype, stream=stream,
+                            return_accumulators=return_accumulators)
+
+
+def _check_w8a8_dtypes(in_dtype, out_dtype, accum_dtype, scale_dtype):
+    if _dt(in_dtype) != torch.int8:
+        raise ValueError("in_dtype must be int8")
+    if _dt(out_dtype) not in (torch.float16, torch.bfloat16):
+        raise ValueError("out_dtype must be float16 or bfloat16")
+    if _dt(accum_dtype) != torch.int32:
+        raise ValueError("accum_dtype must be int32")
+    if _dt(scale_dtype) != torch.float32:
+        raise ValueError("scale_dtype must be float32")
+
+
+@functools.lru_cache(maxsize=None)
+def simple_quant_batch_matmul(Batch: int, M: int, N: int, K: int, scale_size, block_M: int, block_N: int,
+                              block_K: int, in_dtype="int8", out_dtype="float16", accum_dtype="int32",
+                              scale_dtype="float32"):
+    """Factory with the signature of examples/quant_batch_matmul/example_quant_batch_matmul.py:17-22.
+
+    Returns ``kernel(A[Batch,M,K], B[Batch,K,N], scale[N or 1]) -> C[Batch,M,N]``.  Extension: an optional
+    fourth argument ``scale_a`` ([M] or [Batch, M], per-token activation scale, applied before ``scale``)
+    and per-batch ``scale`` of shape [Batch, N].
+    """
+    _check_blocks(block_M, block_N, block_K)
+    _check_w8a8_dtypes(in_dtype, out_dtype, accum_dtype, scale_dtype)
+    if str(scale_size) not in ("1", "N"):
+        raise ValueError('scale_size must be "1" or "N"')
+    return _QuantMatmulKernel(int(Batch), int(M), int(N), int(K), scale_size, _dt(out_dtype))
+
+
+@functools.lru_cache(maxsize=None)
+def simple_quant_matmul(M: int, N: int, K: int, scale_size, block_M: int, block_N: int, block_K: int,
+                        in_dtype="int8", out_dtype="float16", accum_dtype="int32", scale_dtype="float32"):
+    """Factory with the signature of examples/quant_batch_matmul/example_quant_matmul.py:17-22.
+
+    Returns ``kernel(A[M,K], B[K,N], scale[N or 1]) -> C[M,N]`` (optional ``scale_a[M]`` as above).
+    """
+    _check_blocks(block_M, block_N, block_K)
+    _check_w8a8_dtypes(in_dtype, out_dtype, accum_dtype, scale_dtype)
+    if str(scale_size) not in ("1", "N"):
+        raise ValueError('scale_size must be 1 or "N"')
+    return _QuantMatmulKernel(None, int(M), int(N), int(K), scale_size, _dt(out_dtype))
+
+
+# ------------------------------------------------------------------------------------------ W4A16
+_ws_cache = {}
+
+
+def _w4a16_workspace(lib, M, N, K, device, stream_handle):
+    """Scratch buffer (split-K partial sums + arrival counters), one per (device, stream) and size class.
+
+    The counters must start at zero and the kernel leaves them zero, so the buffer is zeroed once, at
+    creation.  Launches on different streams get different buffers because they may overlap on the GPU."""
+    need = lib.qgemm_w4a16_workspace_bytes(M, N, K)
+    if need < 0:
+        raise _lib.QGemmError("qgemm_w4a16_workspace_bytes: " + _lib.last_error())
+    key = (device.index, stream_handle)
+    ws = _ws_cache.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=device)
+        _ws_cache[key] = ws
+    return ws, need
+
+
+def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None, stream=None, status=None):
+    """``C[M,N] = A[M,K] @ W[N,K].T`` with ``W = (unpack_u4(B_packed) - zeros).half() * scales[k // g, n]``
+    (or the raw nibble values when ``scales is None``).  CUDA tensors in, CUDA tensor out."""
+    lib = _lib.load()
+    _require_cuda(A, "A")
+    dev = A.device
+    if A.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError(f"Buffer dtype mismatch for parameter A: expected float16 or bfloat16, got {A.dtype}")
+    out_dtype = A.dtype if out_dtype is None else _dt(out_dtype)
+    if out_dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("output dtype must be float16 or bfloat16")
+    if A.dim() != 2 or B_packed.dim() != 2:
+        raise ValueError("A must be [M, K] and B_packed [N, K/2]")
+    M, K = A.shape
+    N = B_packed.shape[0]
+    _check_tensor(A, 0, "A", A.dtype, (M, K), dev)
+    _check_tensor(B_packed, 1, "B_packed", torch.uint8, (N, K // 2), dev)
+    if K % 2 != 0:
+        raise ValueError("K must be divisible by 2 (INT4 packed format)")
+    if scales is not None:
+        if not isinstance(zeros, int):
+            raise ValueError("zeros must be an integer zero point")
+        if group_size in (-1, None):
+            group_size = K
+        if K % group_size != 0:
+            raise ValueError("group_size must divide K")
+        _check_tensor(scales, 2, "scales", torch.float16, (K // group_size, N), dev)
+    else:
+        zeros, group_size = 0, K
+    sh = _stream_handle(stream, dev)
+    C = torch.empty((M, N), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        ws, need = _w4a16_workspace(lib, M, N, K, dev, sh)
+        rc = lib.qgemm_w4a16(A.data_ptr(), B_packed.data_ptr(), _ptr(scales), int(zeros), int(group_size),
+                             C.data_ptr(), ws.data_ptr(), need, M, N, K, _ABI_DT[A.dtype], _ABI_DT[out_dtype],
+                             _ptr(status), sh)
+    _lib.check(rc, "qgemm_w4a16")
+    return C
+
+
+@functools.lru_cache(maxsize=None)
+def dequant_gemm_fp16_wrapper(M: int, N: int, K: int, block_M: int, block_N: int, block_K: int,
+                              input_dtype: str = "float16", output_dtype: str = "float16"):
+    """Factory with the signature of examples/dequantize_gemm/example_dequant_gemm_fine_grained.py:176-185.
+
+    Returns ``wrapper(A[M,K], B_packed[N,K/2]) -> C[M,N]``.  Like the reference wrapper (:208-221) it takes
+    CPU tensors and returns a CPU tensor; CUDA tensors are accepted too and then the result stays on the
+    GPU.  Extension: ``wrapper(A, B_packed, scales, zeros=8, group_size=128)`` applies group-wise fp16
+    scales of shape [K/group_size, N] and an integer zero point, ``W = (q - zeros) * scales``.
+    """
+    _check_blocks(block_M, block_N, block_K)
+    in_dt, out_dt = _dt(input_dtype), _dt(output_dtype)
+    if in_dt not in (torch.float16, torch.bfloat16) or out_dt not in (torch.float16, torch.bfloat16):
+        raise ValueError("input_dtype / output_dtype must be float16 or bfloat16")
+
+    def wrapper(A: torch.Tensor, B_packed: torch.Tensor, scales=None, zeros: int = 8, group_size: int = 128):
+        if tuple(A.shape) != (M, K) or tuple(B_packed.shape) != (N, K // 2):
+            raise ValueError(f"Static shape mismatch: expected A {(M, K)}, B_packed {(N, K // 2)}; "
+                             f"got {tuple(A.shape)}, {tuple(B_packed.shape)}")
+        if A.dtype != in_dt:
+            raise ValueError(f"Buffer dtype mismatch for parameter A: expected {in_dt}, got {A.dtype}")
+        on_cpu = not A.is_cuda
+        if on_cpu:
+            dev = torch.device("cuda", torch.cuda.current_device())
+            A_, B_ = A.to(dev), B_packed.to(dev)
+            s_ = None if scales is None else scales.to(dev)
+        else:
+            A_, B_, s_ = A, B_packed, scales
+        C = w4a16_gemm(A_, B_, s_, zeros, group_size, out_dtype=out_dt)
+        return C.cpu() if on_cpu else C
+
+    return wrapper
+
+
+# --------------------------------------------------------------------------- W4 -> int8 (exact int32)
+def unpack_int4(B_packed, signed=False, out=None, stream=None):
+    """[N, K/2] uint8 -> [N, K] int8 on the GPU (unsigned 0..15, or two's-complement -8..7 when ``signed``)."""
+    lib = _lib.load()
+    _require_cuda(B_packed, "B_packed")
+    dev = B_packed.device
+    _check_tensor(B_packed, 0, "B_packed", torch.uint8, None, dev)
+    N, K = B_packed.shape[0], B_packed.shape[1] * 2
+    if out is None:
+        out = torch.empty((N, K), dtype=torch.int8, device=dev)
+    else:
+        _check_tensor(out, 1, "out", torch.int8, (N, K), dev)
+    with torch.cuda.device(dev):
+        rc = lib.qgemm_unpack_int4(B_packed.data_ptr(), out.data_ptr(), N, K, 1 if signed else 0,
+                                   _stream_handle(stream, dev))
+    _lib.check(rc, "qgemm_unpack_int4")
+    return out
+
+
+def _w4a8(A, qB, workspace, C, signed, stream=None, status=None):
+    lib = _lib.load()
+    dev = A.device
+    M, K = A.shape
+    N = qB.shape[0]
+    with torch.cuda.device(dev):
+        rc = lib.qgemm_w4a8(A.data_ptr(), qB.data_ptr(), workspace.data_ptr(), C.data_ptr(), M, N, K,
+                            1 if signed else 0, _lib.DT_I32, _ptr(status), _stream_handle(stream, dev))
+    _lib.check(rc, "qgemm_w4a8")
+    return C
+
+
+@functools.lru_cache(maxsize=None)
+def w4a8_gemm_cv(M: int, N: int, K: int):
+    """Factory with the signature of examples/dequantize_gemm/example_dequant_gemm_w4a8.py:26.
+
+    Returns ``kernel(A[M,K] int8, qB[N,K/2] uint8, workspace[N,K] int8, C[M,N] int32) -> C`` with signed
+    (two's-complement) nibbles; like the reference, the caller provides ``workspace`` and ``C`` (:174-177)."""
+
+    def kernel(A, qB, workspace, C, stream=None):
+        _require_cuda(A, "A")
+        dev = A.device
+        _check_tensor(A, 0, "A", torch.int8, (M, K), dev)
+        _check_tensor(qB, 1, "qB", torch.uint8, (N, K // 2), dev)
+        _check_tensor(workspace, 2, "workspace", torch.int8, (N, K), dev)
+        _check_tensor(C, 3, "C", torch.int32, (M, N), dev)
+        return _w4a8(A, qB, workspace, C, signed=True, stream=stream)
+
+    return kernel
+
+
+@functools.lru_cache(maxsize=None)
+def dequant_gemm_int8_wrapper(M: int, N: int, K: int, block_M: int, block_N: int, block_K: int,
+                              output_dtype: str = "int32"):
+    """Factory with the signature of examples/dequantize_gemm/example_dequant_gemm_fine_grained.py:226-234.
+
+    Returns ``wrapper(A[M,K] int8, B_packed[N,K/2] uint8) -> C[M,N]``: unsigned nibbles, exact int32
+    accumulation, then the cast to ``output_dtype`` (int32 / float16 / bfloat16) as the reference does
+    (:263).  CPU tensors in give a CPU tensor out, as in the reference; CUDA tensors stay on the GPU."""
+    _check_blocks(block_M, block_N, block_K)
+    out_dt = _dt(output_dtype)
+    if out_dt not in (torch.int32, torch.float16, torch.bfloat16):
+        raise ValueError("output_dtype must be int32, float16 or bfloat16")
+
+    def wrapper(A: torch.Tensor, B_packed: torch.Tensor):
+        if tuple(A.shape) != (M, K) or tuple(B_packed.shape) != (N, K // 2):
+            raise ValueError(f"Static shape mismatch: expected A {(M, K)}, B_packed {(N, K // 2)}; "
+                             f"got {tuple(A.shape)}, {tuple(B_packed.shape)}")
+        on_cpu = not A.is_cuda
+        dev = torch.device("cuda", torch.cuda.current_device()) if on_cpu else A.device
+        A_, B_ = (A.to(dev), B_packed.to(dev)) if on_cpu else (A, B_packed)
+        _check_tensor(A_, 0, "A", torch.int8, (M, K), dev)
+        _check_tensor(B_, 1, "B_packed", torch.uint8, (N, K // 2), dev)
+        ws = torch.empty((N, K), dtype=torch.int8, device=dev)
+        C = torch.empty((M, N), dtype=torch.int32, device=dev)
+        _w4a8(A_, B_, ws, C, signed=False)
+        C = C.to(out_dt)
+        return C.cpu() if on_cpu else C
+
+    return wrapper
