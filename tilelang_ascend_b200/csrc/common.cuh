@@ -61,11 +61,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Same test, but the hardware may suspend the thread for up to `hint_ns` while the phase is incomplete
+// (fewer issue slots burnt by pollers).
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Shared per-CTA control block for bounded waits.
 struct WaitCtl {
   volatile uint32_t* abort_flag;  // shared memory, set to 1 by the first wait that gives up
   uint32_t* status;               // global memory (nullable)
   uint64_t limit_ns;              // per-wait limit
+  uint32_t hint_ns = 0;           // suspend-time hint for polling (0 = plain try_wait)
 };
 
 // Returns false when the wait gave up (limit exceeded, or another wait of this CTA already gave up).
@@ -74,7 +89,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (ctl.hint_ns ? mbar_try_wait_hint(bar, parity, ctl.hint_ns) : mbar_try_wait(bar, parity)) return true;
     if (((++spins) & 31u) == 0u) {
       if (*ctl.abort_flag) return false;
       if (global_timer_ns() - t0 > ctl.limit_ns) {
@@ -89,6 +104,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
 // Warp-uniform form: lane 0 polls, the result is broadcast, and on success every lane performs its
 // own (immediately successful) try_wait so that each lane has observed the phase itself.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, uint32_t code) {
+  // Fast path: the phase is usually complete already; one test per lane and a vote keep it uniform.
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
   uint32_t ok = 1;
   if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, code) ? 1u : 0u;
   ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -170,6 +187,39 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t adesc, uin
       : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (M rows = lanes, K packed two 16-bit values per
+// 32-bit column, even k in the low half) is read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Warp-convergent forms: every lane executes the call with the same operands (so the compiler can keep
+// them in uniform registers) and only the lane with `leader != 0` issues the instruction.
+__device__ __forceinline__ void umma_f16_ts_elect(uint32_t leader, uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                                  uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_elect(uint32_t leader, uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(leader)
+      : "memory");
+}
+// Ask the TMA unit to bring a tile into L2 only (no shared-memory destination, no completion signal).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(m), "r"(x), "r"(y) : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base lane + i).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -193,6 +243,20 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Registers -> tensor memory: thread i of the warp writes 32 consecutive 32-bit columns of lane (base lane + i).
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ----------------------------------------------------------------- descriptors
 // 64-bit shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets

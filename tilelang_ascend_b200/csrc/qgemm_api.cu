@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "w4a16.cuh"
+#include "w4a16_decode.cuh"
 #include "w8a8.cuh"
 
 namespace {
@@ -58,6 +59,13 @@ int set_smem_w8() {
   if (set_smem(qg::w8a8_gemm_kernel<BN, true, true>, C::SMEM_BYTES)) return -1;
   return 0;
 }
+template <int FLUSH>
+int set_smem_w4d() {
+  using C = qg::W4DCfg;
+  if (set_smem(qg::w4a16_decode_kernel<FLUSH, false>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_decode_kernel<FLUSH, true>, C::SMEM_BYTES)) return -1;
+  return 0;
+}
 template <int MT>
 int set_smem_w4() {
   using C = qg::W4Cfg<MT>;
@@ -86,6 +94,7 @@ int ensure_device(int* sm_count) {
     }
     if (set_smem_w8<128>() || set_smem_w8<256>()) return -1;
     if (set_smem_w4<16>() || set_smem_w4<32>() || set_smem_w4<64>() || set_smem_w4<128>()) return -1;
+    if (set_smem_w4d<0>() || set_smem_w4d<1>() || set_smem_w4d<2>() || set_smem_w4d<4>()) return -1;
     st.sm_count = prop.multiProcessorCount;
     st.ready = true;
   }
@@ -131,7 +140,33 @@ int launch_w4(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUt
   return 0;
 }
 
-int w4_pick_mt(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+template <int FLUSH>
+int launch_w4d(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
+               const qg::W4A16Params& p, int grid, cudaStream_t s) {
+  if (bf)
+    qg::w4a16_decode_kernel<FLUSH, true><<<grid, qg::W4D_THREADS, qg::W4DCfg::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
+  else
+    qg::w4a16_decode_kernel<FLUSH, false><<<grid, qg::W4D_THREADS, qg::W4DCfg::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Token counts up to this use the register-operand streaming kernel (w4a16_decode.cuh); above it the
+// tcgen05 kernel (w4a16.cuh).
+int w4_decode_max_m() {
+  static int v = -1;
+  if (v < 0) {
+    v = 8;
+    if (const char* e = getenv("QGEMM_W4_DECODE_MAX_M")) v = atoi(e) < 8 ? atoi(e) : 8;
+  }
+  return v;
+}
+bool w4_use_decode(int64_t M) { return M <= w4_decode_max_m(); }
+// Token-tile height: 8 for the decode kernel, 16..128 for the tcgen05 kernel.
+int w4_pick_mt(int64_t M) {
+  if (w4_use_decode(M)) return 8;
+  return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+}
 
 constexpr int64_t kW4MaxGrid = 1024;
 constexpr int64_t kW4CounterBytes = kW4MaxGrid * 4;
@@ -274,14 +309,13 @@ int64_t qgemm_w4a16_counter_bytes(void) { return kW4CounterBytes; }
 
 int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   (void)N;
-  (void)K;
   int sms = 0;
   if (ensure_device(&sms)) return -1;
   const int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
   const int mt = w4_pick_mt(M);
   // the arrival counters first (fixed place whatever the tile height), then two partial slots of
-  // [MT][128] fp32 per CTA
-  return kW4CounterBytes + grid * 2 * (int64_t)mt * 128 * 4;
+  // [MT][128] fp32 per CTA, then the f16 copy of the activations in the kernel's K order
+  return kW4CounterBytes + grid * 2 * (int64_t)mt * 128 * 4 + M * K * 2;
 }
 
 int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
@@ -328,11 +362,13 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
     const uint32_t box[2] = {128, (uint32_t)scale_rows};
     if (encode_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
   }
+  const int64_t grid_max = sms < kW4MaxGrid ? sms : kW4MaxGrid;
+  uint8_t* a_prepared = static_cast<uint8_t*>(workspace) + kW4CounterBytes + grid_max * 2 * (int64_t)mt * 128 * 4;
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
     const uint64_t str[1] = {(uint64_t)K * 2};
     const uint32_t box[2] = {64, (uint32_t)mt};
-    if (encode_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, A, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    if (encode_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a_prepared, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
   }
 
   qg::W4A16Params p;
@@ -345,7 +381,6 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
   p.group = (int)(group > (1 << 30) ? (1 << 30) : group);
   p.zero = zero;
   p.has_scales = scales != nullptr;
-  p.a_is_bf16 = a_dtype == QGEMM_DT_BF16;
   p.m_tiles = (int)((M + mt - 1) / mt);
   p.n_tiles = (int)((N + 127) / 128);
   const int64_t num_tiles = (int64_t)p.m_tiles * p.n_tiles;
@@ -354,12 +389,31 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
   p.KS = (int)((K + 255) / 256);
   p.scale_rows = scale_rows;
   p.total_items = num_tiles * p.KS;
+  p.dbg = 0;
+  if (const char* e = getenv("QGEMM_DBG_W4")) p.dbg = atoi(e);
+  p.trace = nullptr;
+  if (const char* e = getenv("QGEMM_TRACE_PTR")) p.trace = reinterpret_cast<unsigned long long*>(strtoull(e, nullptr, 0));
   p.status = status;
   p.wait_limit_ns = g_wait_limit_ns;
   int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
   if (p.total_items < grid) grid = p.total_items;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf = out_dtype == QGEMM_DT_BF16;
+  if (!(p.dbg & 32)) {
+    const long long n_chunks = (long long)M * K / 8;
+    const long long blocks = (n_chunks + 255) / 256;
+    if (blocks > 0x7fffffffll) return fail("qgemm_w4a16: activation tensor too large");
+    qg::w4a16_prepare_activations<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint4*>(A),
+                                                                  reinterpret_cast<uint4*>(a_prepared), n_chunks,
+                                                                  a_dtype == QGEMM_DT_BF16 ? 1 : 0);
+    CUDA_OK(cudaGetLastError());
+  }
+  if (w4_use_decode(M)) {
+    if (scales == nullptr) return launch_w4d<0>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    if (group >= 128) return launch_w4d<4>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    if (group == 64) return launch_w4d<2>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    return launch_w4d<1>(bf, tmW, tmS, tmA, p, (int)grid, s);
+  }
   switch (mt) {
     case 16: return launch_w4<16>(bf, tmW, tmS, tmA, p, (int)grid, s);
     case 32: return launch_w4<32>(bf, tmW, tmS, tmA, p, (int)grid, s);

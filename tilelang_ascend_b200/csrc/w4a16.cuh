@@ -6,17 +6,24 @@
 // tokens are the MMA "N" dimension (MT = 16..128 per tile), so the memory-bound decode shapes stream
 // the packed weights once at full tile height whatever the token count is.
 //
+// The dequantised weights never touch shared memory: each dequant thread owns one weight row, turns
+// 32 bytes of nibbles into 64 f16 values in registers and writes them with tcgen05.st into a ring of
+// tensor-memory columns, from which tcgen05.mma takes its A operand.  Shared memory only holds the
+// packed weights and the (small) activation tiles.
+//
 // Persistent stream-K kernel: the (tile, 256-wide K slab) items are split evenly over the CTAs; a CTA
 // whose slab range covers only part of a tile writes an fp32 partial into scratch memory, and the last
 // contributor of that tile (found with a counter, never by waiting) adds the partials in a fixed order,
 // so results do not depend on arrival order.
 //   warp 0       TMA: packed weights [128 rows x 128 B] + the slab's scales into the "raw" ring
-//   warp 1       tcgen05.mma kind::f16 issuer, fp32 accumulators in tensor memory (double buffered)
-//   warp 2       TMA: activation tiles straight into the operand ring
+//   warp 1       tcgen05.mma kind::f16 issuer (A from TMEM, B from shared memory), fp32 accumulators in
+//                tensor memory, double buffered
+//   warp 2       TMA: activation tiles [MT x 256 k] into their own ring
 //   warps 3..6   epilogue (TMEM -> registers -> global / scratch, split-K reduction)
-//   warps 7..14  dequant: 16 B of nibbles -> lop3 magic-number conversion -> (q - zero) * s in f16x2 ->
-//                swizzled K-major operand tile in shared memory; the same warps permute (and, for
-//                bf16 input, convert) the activation tile in place so both operands share one K order.
+//   warps 7..22  dequant: lop3 magic-number conversion, (q - zero) * s in f16x2, tcgen05.st
+// The conversion emits each group of eight K values in the order 0,4,1,5,2,6,3,7 (what the lop3 pairing
+// gives for free).  A small pre-pass kernel (w4a16_prepare_activations) writes the activations once, in
+// f16 and in that same K order, to scratch memory; the GEMM kernel loads them from there by TMA.
 #pragma once
 
 #include "common.cuh"
@@ -31,34 +38,52 @@ struct W4A16Params {
   int group;            // quantisation group size along K
   int zero;             // integer zero point (0..15)
   int has_scales;       // 0: weights are the raw nibble values (scale 1)
-  int a_is_bf16;        // activations are bf16 (converted to f16 in shared memory) instead of f16
   int m_tiles, n_tiles, num_tiles;
   int KS;               // 256-wide K slabs per tile
   int scale_rows;       // scale rows fetched per slab (256 / group, at least 1)
   long long total_items;
   uint32_t* status;
   unsigned long long wait_limit_ns;
+  int dbg;  // bring-up only: bit 0 skips the dequant arithmetic, bit 1 skips the MMA issue
+  unsigned long long* trace;  // bring-up only: per-item cycle stamps of CTA 0 (8 events per item), nullable
 };
 
+__device__ __forceinline__ void w4_trace(const W4A16Params& p, int item, int ev) {
+  if (p.trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && item < 256) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
+    p.trace[item * 8 + ev] = t;
+  }
+}
+
 constexpr int W4_BN = 128;        // weight rows per tile
-constexpr int W4_SLAB_K = 256;    // K per raw stage: 128 packed bytes per row
-constexpr int W4_HALF_K = 128;    // K per operand stage: two 64-wide swizzle atoms of f16
-constexpr int W4_THREADS = 480;
-constexpr int W4_DQ_WARPS = 8;
+constexpr int W4_SLAB_K = 256;    // K per pipeline item: 128 packed bytes per row
+constexpr int W4_DQ_WARPS = 16;
+constexpr int W4_FIRST_DQ_WARP = 7;
+constexpr int W4_THREADS = (W4_FIRST_DQ_WARP + W4_DQ_WARPS) * 32;  // 736
 constexpr int W4_RAW_PACKED = W4_BN * 128;         // 16 KB
 constexpr int W4_RAW_BYTES = W4_RAW_PACKED + 2048; // + up to 8 scale rows of 128 halves
+constexpr int W4_W_COLS = W4_SLAB_K / 2;           // TMEM columns per slab of dequantised weights
 
 template <int MT>
 struct W4Cfg {
-  static constexpr int RAW_STAGES = (MT <= 64) ? 4 : 3;
-  static constexpr int DEQ_STAGES = (MT <= 64) ? 3 : 2;
-  static constexpr int W_KB_BYTES = W4_BN * 128;  // one 64-wide K block of f16 weights: 16 KB
-  static constexpr int A_KB_BYTES = MT * 128;     // one 64-wide K block of activations
-  static constexpr int DEQ_BYTES = 2 * W_KB_BYTES + 2 * A_KB_BYTES;
-  static constexpr int TMEM_COLS = (2 * MT < 32) ? 32 : 2 * MT;
+  // Ring depths: a slot of the activation ring is recycled only after its item's MMAs have completed,
+  // so that ring must cover the load latency plus the dequant and MMA time of the items in between.
+  static constexpr int RAW_STAGES = (MT == 16) ? 8 : (MT == 32 ? 7 : (MT == 64 ? 5 : 4));
+  static constexpr int A_STAGES = (MT == 16) ? 9 : (MT == 32 ? 6 : (MT == 64 ? 4 : 2));
+  static constexpr int W_STAGES = (MT <= 64) ? 3 : 2;
+  static constexpr int A_KB_BYTES = MT * 128;          // one 64-wide K block of activations
+  static constexpr int A_BYTES = 4 * A_KB_BYTES;       // one 256-wide slab
+  // Consecutive K steps accumulate round-robin into NACC independent accumulators (summed in the
+  // epilogue): with few tokens one MMA is far shorter than its accumulate latency, and a single
+  // accumulator would serialise the whole chain.
+  static constexpr int NACC = 1;
+  static constexpr int ACC_COLS = 2 * NACC * MT;       // two buffers of NACC accumulators
+  static constexpr int TMEM_COLS = 512;
   static constexpr int BAR_BYTES = 512;
-  static constexpr int SMEM_BYTES = RAW_STAGES * W4_RAW_BYTES + DEQ_STAGES * DEQ_BYTES + BAR_BYTES + 1024;
+  static constexpr int SMEM_BYTES = RAW_STAGES * W4_RAW_BYTES + A_STAGES * A_BYTES + BAR_BYTES + 1024;
   static constexpr int CH = (MT < 32) ? 16 : 32;  // accumulator columns per TMEM load
+  static_assert(ACC_COLS + W_STAGES * W4_W_COLS <= 512, "tensor memory budget");
 };
 
 // Contiguous item range of CTA `b` out of `G`: [T*b/G, T*(b+1)/G).
@@ -84,26 +109,25 @@ struct W4SegIter {
 // half2 words (n0,n4) (n1,n5) (n2,n6) (n3,n7): the cheapest order for the magic-number conversion.
 // Low nibbles: 0x6400 | n = 1024 + n, minus (1024 + zero).  High nibbles: 0x6400 | (n << 4) = 1024 + 16 n,
 // times 1/16 minus (64 + zero).  Both are exact; the product with s rounds once (RN), like an f16 multiply.
-__device__ __forceinline__ uint4 w4_dequant8(uint32_t x, uint32_t sub_lo, uint32_t sub_hi, uint32_t s2, bool scaled) {
+__device__ __forceinline__ void w4_dequant8(uint32_t x, uint32_t sub_lo, uint32_t sub_hi, uint32_t s2, bool scaled,
+                                            uint32_t* o) {
   uint32_t lo0, hi0, lo1, hi1;
   const uint32_t y = x >> 8;
-  asm volatile("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(lo0) : "r"(x));
-  asm volatile("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hi0) : "r"(x));
-  asm volatile("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(lo1) : "r"(y));
-  asm volatile("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hi1) : "r"(y));
+  asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(lo0) : "r"(x));
+  asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hi0) : "r"(x));
+  asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(lo1) : "r"(y));
+  asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hi1) : "r"(y));
   const uint32_t sixteenth = 0x2C002C00u;  // 1/16
-  uint4 o;
-  asm volatile("sub.rn.f16x2 %0, %1, %2;" : "=r"(o.x) : "r"(lo0), "r"(sub_lo));
-  asm volatile("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(o.y) : "r"(hi0), "r"(sixteenth), "r"(sub_hi));
-  asm volatile("sub.rn.f16x2 %0, %1, %2;" : "=r"(o.z) : "r"(lo1), "r"(sub_lo));
-  asm volatile("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(o.w) : "r"(hi1), "r"(sixteenth), "r"(sub_hi));
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(o[0]) : "r"(lo0), "r"(sub_lo));
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(o[1]) : "r"(hi0), "r"(sixteenth), "r"(sub_hi));
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(o[2]) : "r"(lo1), "r"(sub_lo));
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(o[3]) : "r"(hi1), "r"(sixteenth), "r"(sub_hi));
   if (scaled) {
-    asm volatile("mul.rn.f16x2 %0, %0, %1;" : "+r"(o.x) : "r"(s2));
-    asm volatile("mul.rn.f16x2 %0, %0, %1;" : "+r"(o.y) : "r"(s2));
-    asm volatile("mul.rn.f16x2 %0, %0, %1;" : "+r"(o.z) : "r"(s2));
-    asm volatile("mul.rn.f16x2 %0, %0, %1;" : "+r"(o.w) : "r"(s2));
+    asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(o[0]) : "r"(s2));
+    asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(o[1]) : "r"(s2));
+    asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(o[2]) : "r"(s2));
+    asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(o[3]) : "r"(s2));
   }
-  return o;
 }
 
 __device__ __forceinline__ uint32_t w4_bf16x2_to_f16x2(uint32_t w) {
@@ -122,6 +146,22 @@ __device__ __forceinline__ uint4 w4_permute_act(uint4 v) {
   return o;
 }
 
+// Pre-pass: activations [M, K] (f16 or bf16) -> f16 with every group of eight K values reordered to
+// 0,4,1,5,2,6,3,7.  One 16-byte chunk per thread.
+__global__ void __launch_bounds__(256)
+w4a16_prepare_activations(const uint4* __restrict__ in, uint4* __restrict__ out, long long n_chunks, int is_bf16) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_chunks) return;
+  uint4 v = in[i];
+  if (is_bf16) {
+    v.x = w4_bf16x2_to_f16x2(v.x);
+    v.y = w4_bf16x2_to_f16x2(v.y);
+    v.z = w4_bf16x2_to_f16x2(v.z);
+    v.w = w4_bf16x2_to_f16x2(v.w);
+  }
+  out[i] = w4_permute_act(v);
+}
+
 __device__ __forceinline__ void w4_epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int MT, bool OUT_BF16>
@@ -130,19 +170,21 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                   const __grid_constant__ CUtensorMap tmA, const W4A16Params p) {
   using Cfg = W4Cfg<MT>;
   constexpr int RS = Cfg::RAW_STAGES;
-  constexpr int DS = Cfg::DEQ_STAGES;
+  constexpr int AS = Cfg::A_STAGES;
+  constexpr int WS = Cfg::W_STAGES;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* raw_base = smem;
-  uint8_t* deq_base = smem + RS * W4_RAW_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(deq_base + DS * Cfg::DEQ_BYTES);
+  uint8_t* a_base = smem + RS * W4_RAW_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(a_base + AS * Cfg::A_BYTES);
   uint64_t* raw_full = bars;
   uint64_t* raw_empty = raw_full + RS;
   uint64_t* a_full = raw_empty + RS;
-  uint64_t* deq_full = a_full + DS;
-  uint64_t* deq_empty = deq_full + DS;
-  uint64_t* tfull = deq_empty + DS;
+  uint64_t* a_empty = a_full + AS;
+  uint64_t* w_full = a_empty + AS;
+  uint64_t* w_empty = w_full + WS;
+  uint64_t* tfull = w_empty + WS;
   uint64_t* tempty = tfull + 2;
   uint64_t* drain = tempty + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
@@ -157,10 +199,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       mbar_init(&raw_full[s], 1);
       mbar_init(&raw_empty[s], W4_DQ_WARPS);
     }
-    for (int s = 0; s < DS; ++s) {
+    for (int s = 0; s < AS; ++s) {
       mbar_init(&a_full[s], 1);
-      mbar_init(&deq_full[s], W4_DQ_WARPS);
-      mbar_init(&deq_empty[s], 1);
+      mbar_init(&a_empty[s], 1);
+    }
+    for (int s = 0; s < WS; ++s) {
+      mbar_init(&w_full[s], W4_DQ_WARPS);
+      mbar_init(&w_empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
@@ -182,7 +227,8 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns};
+  const uint32_t tmem_w = tmem_base + Cfg::ACC_COLS;  // ring of dequantised-weight columns
+  const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns, (uint32_t)(p.dbg >> 8)};
 
   const int G = gridDim.x;
   const int cta = blockIdx.x;
@@ -197,11 +243,21 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
       bool ok = true;
       const uint32_t tx = W4_RAW_PACKED + (p.has_scales ? p.scale_rows * 256 : 0);
+      const int pf = (p.dbg >> 16) & 0xff;  // L2 prefetch distance in slabs
+      int titem = 0;
       while (ok && seg.next(tile, ks0, ks1)) {
         const int n0 = (tile / p.m_tiles) * W4_BN;
         for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(&raw_empty[rs], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           uint8_t* dst = raw_base + rs * W4_RAW_BYTES;
+          // Run ahead of the shared-memory ring in L2: ask for the slab `pf` items further on (same tile
+          // row block if it exists, else the next tile's first slabs; coordinates past the tensor are harmless).
+          if (pf > 0) {
+            const int ksp = ks + pf;
+            if (ksp < p.KS) tma_prefetch_l2_2d(&tmW, ksp * (W4_SLAB_K / 2), n0);
+            else if (tile + 1 < p.num_tiles)
+              tma_prefetch_l2_2d(&tmW, (ksp - p.KS) * (W4_SLAB_K / 2), ((tile + 1) / p.m_tiles) * W4_BN);
+          }
           mbar_arrive_expect_tx(&raw_full[rs], tx);
           tma_load_2d(dst, &tmW, &raw_full[rs], ks * (W4_SLAB_K / 2), n0);
           if (p.has_scales) {
@@ -210,6 +266,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           }
           issued_mask |= 1u << rs;
           parity_mask = (parity_mask & ~(1u << rs)) | (phase << rs);
+          w4_trace(p, titem++, 0);
           if (++rs == RS) { rs = 0; phase ^= 1u; }
         }
       }
@@ -229,27 +286,25 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   } else if (warp == 2) {
     // ------------------------------------------------- activation producer
     if (lane == 0) {
-      int ds = 0;
+      int as = 0;
       uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
       bool ok = true;
       while (ok && seg.next(tile, ks0, ks1)) {
         const int m0 = (tile % p.m_tiles) * MT;
-        for (int ks = ks0; ok && ks < ks1; ++ks) {
-          for (int h = 0; h < 2; ++h) {
-            if (!mbar_wait(&deq_empty[ds], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
-            uint8_t* dstA = deq_base + ds * Cfg::DEQ_BYTES + 2 * Cfg::W_KB_BYTES;
-            mbar_arrive_expect_tx(&a_full[ds], 2 * Cfg::A_KB_BYTES);
-            const int k0 = ks * W4_SLAB_K + h * W4_HALF_K;
-            tma_load_2d(dstA, &tmA, &a_full[ds], k0, m0);
-            tma_load_2d(dstA + Cfg::A_KB_BYTES, &tmA, &a_full[ds], k0 + 64, m0);
-            issued_mask |= 1u << ds;
-            parity_mask = (parity_mask & ~(1u << ds)) | (phase << ds);
-            if (++ds == DS) { ds = 0; phase ^= 1u; }
-          }
+        for (int ks = ks0; ks < ks1; ++ks) {
+          if (!mbar_wait(&a_empty[as], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* dstA = a_base + as * Cfg::A_BYTES;
+          mbar_arrive_expect_tx(&a_full[as], Cfg::A_BYTES);
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)
+            tma_load_2d(dstA + kb * Cfg::A_KB_BYTES, &tmA, &a_full[as], ks * W4_SLAB_K + kb * 64, m0);
+          issued_mask |= 1u << as;
+          parity_mask = (parity_mask & ~(1u << as)) | (phase << as);
+          if (++as == AS) { as = 0; phase ^= 1u; }
         }
       }
       if (!ok) {
-        for (int s = 0; s < DS; ++s) {
+        for (int s = 0; s < AS; ++s) {
           if (!(issued_mask & (1u << s))) continue;
           const uint64_t t0 = global_timer_ns();
           while (!mbar_try_wait(&a_full[s], (parity_mask >> s) & 1u)) {
@@ -263,41 +318,51 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop with identical (warp-uniform) operands; lane 0 issues.
+    {
       constexpr uint32_t idesc = make_idesc(ACC_F32, FMT_F16, FMT_F16, 0, 0, W4_BN, MT);
-      int ds = 0;
-      uint32_t phase = 0;
-      int it = 0;
+      const uint32_t leader = (lane == 0) ? 1u : 0u;
+      // K-major activation descriptor without its start-address field (filled in per stage).
+      const uint64_t desc_hi = make_desc_kmajor(0);
+      const uint32_t a_base_u32 = smem_u32(a_base);
+      int ws = 0, as = 0;
+      uint32_t wphase = 0, aphase = 0;
+      int it = 0, titem = 0;
       bool ok = true;
       while (ok && seg.next(tile, ks0, ks1)) {
         const int buf = it & 1;
         const uint32_t tphase = (it >> 1) & 1;
-        if (!mbar_wait(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+        if (!mbar_wait_warp(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t d = tmem_base + buf * MT;
-        uint32_t acc = 0;
-        for (int i = 0; ok && i < 2 * (ks1 - ks0); ++i) {
-          if (!mbar_wait(&deq_full[ds], phase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+        const uint32_t d = tmem_base + buf * (Cfg::NACC * MT);
+        uint32_t started = 0;  // bit a set once accumulator a has been written in this segment
+        for (int ks = ks0; ks < ks1; ++ks) {
+          if (!mbar_wait_warp(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+          if (!mbar_wait_warp(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t sW = smem_u32(deq_base + ds * Cfg::DEQ_BYTES);
-          const uint32_t sA = sW + 2 * Cfg::W_KB_BYTES;
+          w4_trace(p, titem, 5);
+          const uint64_t adesc0 = desc_hi | (uint64_t)(((a_base_u32 + as * Cfg::A_BYTES) & 0x3FFFFu) >> 4);
+          const uint32_t tW = tmem_w + ws * W4_W_COLS;
+          if (!(p.dbg & 2)) {
 #pragma unroll
-          for (int kb = 0; kb < 2; ++kb) {
-            const uint64_t wd = make_desc_kmajor(sW + kb * Cfg::W_KB_BYTES);
-            const uint64_t ad = make_desc_kmajor(sA + kb * Cfg::A_KB_BYTES);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {  // 16 f16 = 32 bytes per MMA
-              umma_f16_ss(d, wd + (uint64_t)(2 * k), ad + (uint64_t)(2 * k), idesc, acc);
-              acc = 1;
+            for (int kk = 0; kk < W4_SLAB_K / 16; ++kk) {  // 16 k per MMA: 8 TMEM columns, 32 bytes of smem
+              constexpr int NA = Cfg::NACC;
+              const int a = kk & (NA - 1);
+              const uint32_t off = (uint32_t)(((kk >> 2) * Cfg::A_KB_BYTES + (kk & 3) * 32) >> 4);
+              umma_f16_ts_elect(leader, d + a * MT, tW + kk * 8, adesc0 + off, idesc, (started >> a) & 1u);
+              started |= 1u << a;
             }
           }
-          umma_commit(&deq_empty[ds]);
-          if (++ds == DS) { ds = 0; phase ^= 1u; }
+          umma_commit_elect(leader, &w_empty[ws]);
+          umma_commit_elect(leader, &a_empty[as]);
+          w4_trace(p, titem++, 6);
+          if (++ws == WS) { ws = 0; wphase ^= 1u; }
+          if (++as == AS) { as = 0; aphase ^= 1u; }
         }
-        if (ok) umma_commit(&tfull[buf]);
+        if (ok) umma_commit_elect(leader, &tfull[buf]);
         ++it;
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         umma_commit(drain);
         const uint64_t t0 = global_timer_ns();
         while (!mbar_try_wait(drain, 0)) {
@@ -305,7 +370,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
       }
     }
-  } else if (warp >= 3 && warp < 7) {
+  } else if (warp >= 3 && warp < W4_FIRST_DQ_WARP) {
     // ---------------------------------------------------------------- epilogue
     constexpr int CH = Cfg::CH;
     const int q = warp & 3;
@@ -323,13 +388,22 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const bool ok = mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE);
       if (ok) {
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * MT;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (Cfg::NACC * MT);
+        constexpr int nacc = Cfg::NACC;
 #pragma unroll 1
         for (int c = 0; c < MT / CH; ++c) {
           uint32_t r[CH];
           if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + c * CH, r);
           else tmem_ld_32x32b_x32(taddr + c * CH, r);
           tmem_ld_wait();
+          for (int a = 1; a < nacc; ++a) {
+            uint32_t r2[CH];
+            if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + a * MT + c * CH, r2);
+            else tmem_ld_32x32b_x32(taddr + a * MT + c * CH, r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+          }
           if (full_tile) {
             if (n < p.N) {
 #pragma unroll
@@ -381,85 +455,105 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       if (is_last) {
         __threadfence();
         if (n < p.N) {
-          for (int m = 0; m < MT && m0 + m < p.M; ++m) {
-            float sum = 0.0f;
+          // Fixed summation order (contributor b_first .. b_last); per contributor all MT loads are issued
+          // before the first add so that their latencies overlap.
+          constexpr int RU = 16;
+          const int rows = min(MT, p.M - m0);
+#pragma unroll 1
+          for (int mb = 0; mb < rows; mb += RU) {
+            float sum[RU];
+#pragma unroll
+            for (int u = 0; u < RU; ++u) sum[u] = 0.0f;
+#pragma unroll 1
             for (int c = b_first; c <= b_last; ++c) {
               const long long c_end = w4_range_begin(T, G, c + 1);
-              const bool reaches_end = c_end >= first_item + p.KS;
-              const int slot = reaches_end ? 2 * c : 2 * c + 1;
-              sum += __ldcg(p.ws_partials + (size_t)slot * (MT * W4_BN) + (size_t)m * W4_BN + nl);
+              const int slot = (c_end >= first_item + p.KS) ? 2 * c : 2 * c + 1;
+              const float* src = p.ws_partials + (size_t)slot * (MT * W4_BN) + (size_t)mb * W4_BN + nl;
+              float v[RU];
+#pragma unroll
+              for (int u = 0; u < RU; ++u) v[u] = (mb + u < rows) ? __ldcg(src + u * W4_BN) : 0.0f;
+#pragma unroll
+              for (int u = 0; u < RU; ++u) sum[u] += v[u];
             }
-            Cout[(size_t)(m0 + m) * p.N + n] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum))
-                                                       : __half_as_ushort(__float2half_rn(sum));
+#pragma unroll
+            for (int u = 0; u < RU; ++u) {
+              if (mb + u < rows)
+                Cout[(size_t)(m0 + mb + u) * p.N + n] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum[u]))
+                                                                : __half_as_ushort(__float2half_rn(sum[u]));
+            }
           }
         }
       }
     }
-  } else if (warp >= 7) {
+  } else if (warp >= W4_FIRST_DQ_WARP) {
     // ----------------------------------------------------------------- dequant
-    const int wd = warp - 7;
-    const int tid_d = wd * 32 + lane;
-    const int rr = lane >> 2;
-    const int c4 = lane & 3;
-    const int row_lo = wd * 8 + (((rr & 1) << 2) | (rr >> 1));  // rows r, r+4 share a quarter-warp: no bank conflicts
-    const int sw = row_lo & 7;
+    // Warp (q, j): TMEM lanes 32q..32q+31 (the quadrant this warp may touch), K sub-range [64j, 64j+64) of
+    // the slab = packed 16-byte chunks 2j and 2j+1 of the row = 32 TMEM columns.
+    const int wd = warp - W4_FIRST_DQ_WARP;
+    const int q = warp & 3;
+    const int j = wd >> 2;
+    const int row = q * 32 + lane;
+    const int sw = row & 7;
+    const uint32_t off0 = row * 128 + (((2 * j) ^ sw) << 4);      // quarter-warps read 8 rows x 8 distinct chunks
+    const uint32_t off1 = row * 128 + (((2 * j + 1) ^ sw) << 4);
     const uint32_t zero = (uint32_t)p.zero;
     const uint32_t sub_lo = (0x6400u + zero) * 0x00010001u;                      // (1024 + zero) x2
     const uint32_t sub_hi = ((0x5400u + (zero << 4)) | 0x8000u) * 0x00010001u;   // -(64 + zero) x2
     const bool scaled = p.has_scales != 0;
-    int rs = 0, ds = 0;
-    uint32_t rphase = 0, dphase = 0;
+    const int srow0 = (p.group <= W4_SLAB_K) ? (64 * j) / p.group : 0;
+    const int srow1 = (p.group <= W4_SLAB_K) ? (64 * j + 32) / p.group : 0;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    int rs = 0, ws = 0, titem = 0;
+    uint32_t rphase = 0, wphase = 0;
     bool ok = true;
+    const bool tr_first = (wd == 0), tr_last = (wd == W4_DQ_WARPS - 1);
     while (ok && seg.next(tile, ks0, ks1)) {
-      for (int ks = ks0; ok && ks < ks1; ++ks) {
+      for (int ks = ks0; ks < ks1; ++ks) {
         if (!mbar_wait_warp(&raw_full[rs], rphase, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
+        if (tr_first) w4_trace(p, titem, 1);
+        if (tr_last) w4_trace(p, titem, 7);
         const uint8_t* rawp = raw_base + rs * W4_RAW_BYTES;
-        const __half* sS = reinterpret_cast<const __half*>(rawp + W4_RAW_PACKED);
-        for (int h = 0; h < 2; ++h) {
-          if (!mbar_wait_warp(&deq_empty[ds], dphase ^ 1u, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
-          uint8_t* dW = deq_base + ds * Cfg::DEQ_BYTES + (c4 >> 1) * Cfg::W_KB_BYTES;
-          const int chunk = 4 * h + c4;          // 16-byte packed chunk of the 128-byte row
-          const int kloc = h * W4_HALF_K + c4 * 32;
-          const int srow = (p.group <= W4_SLAB_K) ? kloc / p.group : 0;
-#pragma unroll
-          for (int pass = 0; pass < 2; ++pass) {
-            const int row = row_lo + pass * 64;
-            const uint4 v = *reinterpret_cast<const uint4*>(rawp + row * 128 + ((chunk ^ sw) << 4));
-            uint32_t s2 = 0x3C003C00u;
-            if (scaled) s2 = (uint32_t)__half_as_ushort(sS[srow * W4_BN + row]) * 0x00010001u;
-            const uint32_t xs[4] = {v.x, v.y, v.z, v.w};
-            uint8_t* drow = dW + row * 128;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 o = w4_dequant8(xs[j], sub_lo, sub_hi, s2, scaled);
-              *reinterpret_cast<uint4*>(drow + (((((c4 & 1) << 2) + j) ^ sw) << 4)) = o;
-            }
-          }
-          // Activations for this stage: permute K inside every group of eight (and convert bf16 -> f16) in place.
-          if (!mbar_wait_warp(&a_full[ds], dphase, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
-          uint4* aT = reinterpret_cast<uint4*>(deq_base + ds * Cfg::DEQ_BYTES + 2 * Cfg::W_KB_BYTES);
-#pragma unroll
-          for (int i = 0; i < (2 * Cfg::A_KB_BYTES / 16 + 255) / 256; ++i) {
-            const int idx = tid_d + i * 256;
-            if (idx < 2 * Cfg::A_KB_BYTES / 16) {
-              uint4 v = aT[idx];
-              if (p.a_is_bf16) {
-                v.x = w4_bf16x2_to_f16x2(v.x);
-                v.y = w4_bf16x2_to_f16x2(v.y);
-                v.z = w4_bf16x2_to_f16x2(v.z);
-                v.w = w4_bf16x2_to_f16x2(v.w);
-              }
-              aT[idx] = w4_permute_act(v);
-            }
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&deq_full[ds]);
-          if (++ds == DS) { ds = 0; dphase ^= 1u; }
+        const uint4 v0 = *reinterpret_cast<const uint4*>(rawp + off0);
+        const uint4 v1 = *reinterpret_cast<const uint4*>(rawp + off1);
+        uint32_t s20 = 0x3C003C00u, s21 = 0x3C003C00u;
+        if (scaled) {
+          const __half* sS = reinterpret_cast<const __half*>(rawp + W4_RAW_PACKED);
+          s20 = (uint32_t)__half_as_ushort(sS[srow0 * W4_BN + row]) * 0x00010001u;
+          s21 = (uint32_t)__half_as_ushort(sS[srow1 * W4_BN + row]) * 0x00010001u;
         }
+        uint32_t o[32];
+        if (p.dbg & 1) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = v0.x + i;
+        } else {
+        w4_dequant8(v0.x, sub_lo, sub_hi, s20, scaled, o + 0);
+        w4_dequant8(v0.y, sub_lo, sub_hi, s20, scaled, o + 4);
+        w4_dequant8(v0.z, sub_lo, sub_hi, s20, scaled, o + 8);
+        w4_dequant8(v0.w, sub_lo, sub_hi, s20, scaled, o + 12);
+        w4_dequant8(v1.x, sub_lo, sub_hi, s21, scaled, o + 16);
+        w4_dequant8(v1.y, sub_lo, sub_hi, s21, scaled, o + 20);
+        w4_dequant8(v1.z, sub_lo, sub_hi, s21, scaled, o + 24);
+        w4_dequant8(v1.w, sub_lo, sub_hi, s21, scaled, o + 28);
+        }
+        // the packed bytes are in registers: hand the raw stage back to the producer
         __syncwarp();
-        if (ok && lane == 0) mbar_arrive(&raw_empty[rs]);
+        if (lane == 0) mbar_arrive(&raw_empty[rs]);
         if (++rs == RS) { rs = 0; rphase ^= 1u; }
+        if (tr_first) w4_trace(p, titem, 2);
+
+        if (!mbar_wait_warp(&w_empty[ws], wphase ^ 1u, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (tr_first) w4_trace(p, titem, 3);
+        if (!(p.dbg & 16)) {
+          tmem_st_32x32b_x32(tmem_w + lane_addr + ws * W4_W_COLS + j * 32, o);
+          tmem_st_wait();
+        }
+        tc_fence_before_sync();
+        if (tr_first) w4_trace(p, titem, 4);
+        ++titem;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&w_full[ws]);
+        if (++ws == WS) { ws = 0; wphase ^= 1u; }
       }
     }
   }

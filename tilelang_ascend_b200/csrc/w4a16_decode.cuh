@@ -1,0 +1,308 @@
+// W4A16 decode variant (few tokens, memory bound) for sm_100a.
+//
+// With at most 8 tokens the GEMM is a weight stream: every packed byte is read once from HBM and used for a
+// handful of tokens.  Measured on B200, tcgen05.mma with a 16-token N costs about 94 cycles per K=16 step
+// whatever the accumulator layout (fixed tensor-memory operand/accumulator traffic per instruction), i.e.
+// 0.8 us per 16 KB of packed weights against 0.37 us of HBM time, so this variant keeps the weights in
+// registers all the way: TMA ring -> 4-byte shared-memory loads -> lop3 conversion -> mma.sync.m16n8k16
+// with the weights as the register A operand.  The tcgen05 kernel in w4a16.cuh serves larger token counts.
+//
+//   warp 0        TMA producer: per 256-wide K slab one stage = packed weights [128 rows x 128 B],
+//                 the slab's scales, and the prepared activations [MT tokens x 256 k]
+//   warps 1..16   compute: warp (rb, kh) owns weight rows 16*rb .. 16*rb+15 and the K half kh of every slab
+//
+// Numerics: products (q - zero) * a are exact in the tensor core and accumulate in fp32 per quantisation
+// group; the group's fp32 sum is then multiplied by the group scale.  With one token set to a unit vector
+// this reproduces half(q - zero) * s bit for bit; in general it differs from multiplying each weight by the
+// scale in f16 first only by that product's own rounding (2^-11 relative per term).
+// The activations come from the same pre-pass as in w4a16.cuh (f16, every group of eight K values in the
+// order 0,4,1,5,2,6,3,7), which is exactly the pairing the lop3 conversion produces.
+#pragma once
+
+#include "common.cuh"
+#include "w4a16.cuh"
+
+namespace qg {
+
+constexpr int W4D_CWARPS = 16;
+constexpr int W4D_THREADS = (1 + W4D_CWARPS) * 32;  // 544
+constexpr int W4D_CTHREADS = W4D_CWARPS * 32;       // 512
+
+struct W4DCfg {
+  static constexpr int MT = 8;                                // tokens per tile (one mma.sync N)
+  static constexpr int A_KB_BYTES = MT * 128;                 // one 64-wide K block of activations
+  static constexpr int STAGE_BYTES = W4_RAW_BYTES + 4 * A_KB_BYTES;
+  static constexpr int STAGES = 9;
+  static constexpr int RED_BYTES = MT * W4_BN * 4;            // fp32 tile for the K-half exchange / epilogue
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RED_BYTES + BAR_BYTES + 1024;
+};
+
+// Eight nibbles of x -> (n - zero) as f16 pairs (n0,n4) (n1,n5) (n2,n6) (n3,n7); no scale.
+__device__ __forceinline__ void w4d_convert8(uint32_t x, uint32_t sub_lo, uint32_t sub_hi, uint32_t (&h)[4]) {
+  uint32_t lo0, hi0, lo1, hi1;
+  const uint32_t y = x >> 8;
+  asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(lo0) : "r"(x));
+  asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hi0) : "r"(x));
+  asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xea;" : "=r"(lo1) : "r"(y));
+  asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xea;" : "=r"(hi1) : "r"(y));
+  const uint32_t sixteenth = 0x2C002C00u;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(h[0]) : "r"(lo0), "r"(sub_lo));
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(h[1]) : "r"(hi0), "r"(sixteenth), "r"(sub_hi));
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(h[2]) : "r"(lo1), "r"(sub_lo));
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(h[3]) : "r"(hi1), "r"(sixteenth), "r"(sub_hi));
+}
+
+// D(16x8, fp32) = A(16x16, f16, row) * B(16x8, f16, col) + C
+__device__ __forceinline__ void w4d_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1, const float (&c)[4]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%10, %11, %12, %13};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+__device__ __forceinline__ void w4d_cbar() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+
+// FLUSH: number of 32-wide K chunks per quantisation group inside a warp's 128-wide K half (4 when the
+// group is 128 or larger, 2 for 64, 1 for 32); 0 = no scales (raw nibble values).
+template <int FLUSH, bool OUT_BF16>
+__global__ void __launch_bounds__(W4D_THREADS, 1)
+w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
+                    const __grid_constant__ CUtensorMap tmA, const W4A16Params p) {
+  using Cfg = W4DCfg;
+  constexpr int MT = Cfg::MT;
+  constexpr int ST = Cfg::STAGES;
+  constexpr bool SCALED = FLUSH != 0;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* red = reinterpret_cast<float*>(smem + ST * Cfg::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ST * Cfg::STAGE_BYTES + Cfg::RED_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + ST;
+  volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(empty + ST);
+  volatile uint32_t* epi_flag = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], W4D_CWARPS);
+    }
+    *abort_flag = 0;
+    *epi_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmA);
+    if (SCALED) tma_prefetch_desc(&tmS);
+  }
+  __syncthreads();
+  const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns, 0};
+
+  const int G = gridDim.x;
+  const int cta = blockIdx.x;
+  const long long T = p.total_items;
+  W4SegIter seg{w4_range_begin(T, G, cta), w4_range_begin(T, G, cta + 1), p.KS};
+  int tile, ks0, ks1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
+      bool ok = true;
+      const uint32_t tx = W4_RAW_PACKED + (SCALED ? p.scale_rows * 256 : 0) + 4 * Cfg::A_KB_BYTES;
+      while (ok && seg.next(tile, ks0, ks1)) {
+        const int n0 = (tile / p.m_tiles) * W4_BN;
+        const int m0 = (tile % p.m_tiles) * MT;
+        for (int ks = ks0; ks < ks1; ++ks) {
+          if (!mbar_wait(&empty[s], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* dst = smem + s * Cfg::STAGE_BYTES;
+          mbar_arrive_expect_tx(&full[s], tx);
+          tma_load_2d(dst, &tmW, &full[s], ks * (W4_SLAB_K / 2), n0);
+          if (SCALED) {
+            const int srow = (p.group <= W4_SLAB_K) ? ks * p.scale_rows : (ks * W4_SLAB_K) / p.group;
+            tma_load_2d(dst + W4_RAW_PACKED, &tmS, &full[s], n0, srow);
+          }
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)
+            tma_load_2d(dst + W4_RAW_BYTES + kb * Cfg::A_KB_BYTES, &tmA, &full[s], ks * W4_SLAB_K + kb * 64, m0);
+          issued_mask |= 1u << s;
+          parity_mask = (parity_mask & ~(1u << s)) | (phase << s);
+          if (++s == ST) { s = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < ST; ++i) {
+          if (!(issued_mask & (1u << i))) continue;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(&full[i], (parity_mask >> i) & 1u)) {
+            if (global_timer_ns() - t0 > p.wait_limit_ns) {
+              if (p.status) atomicMax(p.status, (uint32_t)ST_TIMEOUT_DRAIN);
+              break;
+            }
+          }
+        }
+      }
+    }
+    return;  // the producer warp takes no part in the compute warps' named barrier
+  }
+
+  // ------------------------------------------------------------------ compute warps
+  const int cw = warp - 1;
+  const int rb = cw & 7;    // 16-row block of the tile
+  const int kh = cw >> 3;   // K half of every slab
+  const int g = lane >> 2;  // mma "group id": weight row g / g+8, token g
+  const int c = lane & 3;   // mma "thread in group": K pairs and token pairs
+  const int ctid = cw * 32 + lane;
+  const uint32_t zero = (uint32_t)p.zero;
+  const uint32_t sub_lo = (0x6400u + zero) * 0x00010001u;
+  const uint32_t sub_hi = ((0x5400u + (zero << 4)) | 0x8000u) * 0x00010001u;
+  // Per-thread byte offsets inside a stage, fixed for the whole kernel.  Chunk ch = 4*kh + kc is the
+  // 16-byte (32 k) piece of the 128-byte packed row; the activation piece of the same 32 k sits in K block
+  // ch/2 at 16-byte position (ch&1)*4 + c of token row g; both tiles are 128-byte swizzled by (row & 7) = g.
+  uint32_t w_off[4], a_off[4];
+#pragma unroll
+  for (int kc = 0; kc < 4; ++kc) {
+    const int ch = 4 * kh + kc;
+    w_off[kc] = (uint32_t)((16 * rb + g) * 128 + 4 * c + ((ch ^ g) << 4));
+    a_off[kc] = (uint32_t)(W4_RAW_BYTES + (ch >> 1) * Cfg::A_KB_BYTES + g * 128 + (((((ch & 1) << 2) + c) ^ g) << 4));
+  }
+  // scale of this warp's K half: row of the stage's scale tile for chunk kc (groups up to 256 are powers of two)
+  const int gshift = 31 - __clz(p.group);
+  const bool small_group = p.group <= W4_SLAB_K;
+  const uint32_t s_off = (uint32_t)(W4_RAW_PACKED + (16 * rb + g) * 2);
+  uint16_t* Cout = reinterpret_cast<uint16_t*>(p.C);
+  const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
+
+  int s = 0;
+  uint32_t phase = 0;
+  bool ok = true;
+  while (seg.next(tile, ks0, ks1)) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc2[4] = {0.f, 0.f, 0.f, 0.f};  // second chain when unscaled
+
+    for (int ks = ks0; ks < ks1; ++ks) {
+      if (ok) ok = mbar_wait_warp(&full[s], phase, ctl, ST_TIMEOUT_DEQUANT);
+      if (ok) {
+        const uint8_t* stg = smem + s * Cfg::STAGE_BYTES;
+        float pa[4], pb[4];  // two independent accumulation chains per group
+#pragma unroll
+        for (int kc = 0; kc < 4; ++kc) {
+          const uint32_t x_lo = *reinterpret_cast<const uint32_t*>(stg + w_off[kc]);
+          const uint32_t x_hi = *reinterpret_cast<const uint32_t*>(stg + w_off[kc] + 8 * 128);
+          const uint4 av = *reinterpret_cast<const uint4*>(stg + a_off[kc]);
+          uint32_t hl[4], hh[4];
+          w4d_convert8(x_lo, sub_lo, sub_hi, hl);
+          w4d_convert8(x_hi, sub_lo, sub_hi, hh);
+          if constexpr (!SCALED) {
+            w4d_mma(acc, hl[0], hh[0], hl[1], hh[1], av.x, av.y, acc);
+            w4d_mma(acc2, hl[2], hh[2], hl[3], hh[3], av.z, av.w, acc2);
+          } else {
+            if (kc % FLUSH == 0) {
+              w4d_mma(pa, hl[0], hh[0], hl[1], hh[1], av.x, av.y, zero4);
+              w4d_mma(pb, hl[2], hh[2], hl[3], hh[3], av.z, av.w, zero4);
+            } else {
+              w4d_mma(pa, hl[0], hh[0], hl[1], hh[1], av.x, av.y, pa);
+              w4d_mma(pb, hl[2], hh[2], hl[3], hh[3], av.z, av.w, pb);
+            }
+            if ((kc + 1) % FLUSH == 0) {
+              // end of a quantisation group (or of this warp's 128 k of a larger group): scale the partial sums
+              const int srow = small_group ? ((kh * 128 + kc * 32) >> gshift) : 0;
+              const __half* sp = reinterpret_cast<const __half*>(stg + s_off) + srow * W4_BN;
+              const float s_lo = __half2float(sp[0]);
+              const float s_hi = __half2float(sp[8]);
+              acc[0] = fmaf(pa[0] + pb[0], s_lo, acc[0]);
+              acc[1] = fmaf(pa[1] + pb[1], s_lo, acc[1]);
+              acc[2] = fmaf(pa[2] + pb[2], s_hi, acc[2]);
+              acc[3] = fmaf(pa[3] + pb[3], s_hi, acc[3]);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+      }
+      if (++s == ST) { s = 0; phase ^= 1u; }
+    }
+    if constexpr (!SCALED) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
+    }
+
+    // ---- segment end: add the two K halves in shared memory, then write the tile or its partial sum
+    const bool full_tile = (ks0 == 0 && ks1 == p.KS);
+    const int n0 = (tile / p.m_tiles) * W4_BN;
+    const int m0 = (tile % p.m_tiles) * MT;
+    float* r0 = red + (2 * c) * W4_BN + 16 * rb + g;
+    if (kh == 1) {
+      r0[0] = acc[0];
+      r0[W4_BN] = acc[1];
+      r0[8] = acc[2];
+      r0[W4_BN + 8] = acc[3];
+    }
+    w4d_cbar();
+    if (kh == 0) {
+      r0[0] += acc[0];
+      r0[W4_BN] += acc[1];
+      r0[8] += acc[2];
+      r0[W4_BN + 8] += acc[3];
+    }
+    w4d_cbar();
+    if (*abort_flag) break;  // uniform: read after the barrier
+    const int rows = min(MT, p.M - m0);
+    if (full_tile) {
+      for (int idx = ctid; idx < rows * W4_BN; idx += W4D_CTHREADS) {
+        const int m = idx >> 7, nl = idx & 127;
+        if (n0 + nl < p.N) {
+          const float v = red[idx];
+          Cout[(size_t)(m0 + m) * p.N + n0 + nl] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
+                                                            : __half_as_ushort(__float2half_rn(v));
+        }
+      }
+      w4d_cbar();  // `red` is reused by the next segment
+      continue;
+    }
+    // Split tile: publish the partial, count arrivals; the last contributor reduces in a fixed order.
+    const int my_slot = (ks1 < p.KS) ? 2 * cta + 1 : 2 * cta;
+    float* my_part = p.ws_partials + (size_t)my_slot * (MT * W4_BN);
+    for (int idx = ctid; idx < rows * W4_BN; idx += W4D_CTHREADS) my_part[idx] = red[idx];
+    const long long first_item = (long long)tile * p.KS;
+    const int b_first = w4_owner(T, G, first_item);
+    const int b_last = w4_owner(T, G, first_item + p.KS - 1);
+    __threadfence();
+    w4d_cbar();
+    if (ctid == 0) {
+      uint32_t last = 0;
+      const uint32_t old = atomicAdd(p.ws_counters + b_first, 1u);
+      if (old == (uint32_t)(b_last - b_first)) {
+        last = 1;
+        p.ws_counters[b_first] = 0;  // every contributor has arrived: leave the counter clean
+      }
+      *epi_flag = last;
+    }
+    w4d_cbar();
+    const bool is_last = *epi_flag != 0;
+    w4d_cbar();  // epi_flag and `red` may be rewritten only after everyone has read them
+    if (is_last) {
+      __threadfence();
+      for (int idx = ctid; idx < rows * W4_BN; idx += W4D_CTHREADS) {
+        const int m = idx >> 7, nl = idx & 127;
+        float sum = 0.f;
+        for (int cc = b_first; cc <= b_last; ++cc) {  // fixed order: results do not depend on arrival order
+          const long long c_end = w4_range_begin(T, G, cc + 1);
+          const int slot = (c_end >= first_item + p.KS) ? 2 * cc : 2 * cc + 1;
+          sum += __ldcg(p.ws_partials + (size_t)slot * (MT * W4_BN) + idx);
+        }
+        if (n0 + nl < p.N)
+          Cout[(size_t)(m0 + m) * p.N + n0 + nl] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum))
+                                                            : __half_as_ushort(__float2half_rn(sum));
+      }
+    }
+  }
+}
+
+}  // namespace qg
