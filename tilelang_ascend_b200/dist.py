@@ -71,8 +71,8 @@ class ColumnShardedW4A16:
         if not gather or self.world == 1:
             return C_local
         M, nl = C_local.shape
-        parts = torch.empty((self.world, M, nl), dtype=C_local.dtype, device=C_local.device)
-        dist.all_gather_into_tensor(parts, C_local, group=self.pg)
-        return parts.permute(1, 0, 2).reshape(M, self.world * nl)
+        parts = torch.empty((self.world * M, nl), dtype=C_local.dtype, device=C_local.device)
+        dist.all_gather_into_tensor(parts, C_local, group=self.pg)  # rank r's block lands in rows [r*M, (r+1)*M)
+        return parts.view(self.world, M, nl).permute(1, 0, 2).reshape(M, self.world * nl)
 
     __call__ = forward
