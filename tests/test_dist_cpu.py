@@ -70,6 +70,8 @@ def _worker_peer_leaves(rank, world, port, q):
         dist.all_reduce(t)  # step 1: everybody present
         if rank == 1:
             q.put((rank, True, "left"))
+            q.close()
+            q.join_thread()  # make sure the message is out before the process disappears
             os._exit(0)
         try:
             dist.all_reduce(t)  # step 2: the peer is gone
