@@ -109,6 +109,33 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
                 int out_dtype, uint32_t* status, void* stream);
 
 /*
+ * W4A16 dequantize-GEMM that needs no memory from the caller beyond inputs and output.  (No counterpart
+ * in the reference: there the wrapper allocates every workspace with torch before the call.)
+ *
+ * Meant for hosts that are not allowed to allocate device memory where the operator runs: an
+ * inference-runtime plugin whose execute hook is handed only its tensors and must not call cudaMalloc
+ * (the runtime has planned all memory up front, and an allocation there would stall the whole device),
+ * or a plain C / FFI caller that owns nothing but its input and output buffers.  Same arguments and
+ * results as qgemm_w4a16 without the workspace: the scratch memory is an array inside the library
+ * image, QGEMM_W4A16_NOALLOC_SCRATCH_MB megabytes on every GPU that loads the library, held until the
+ * process exits.
+ *
+ * Limits: M <= QGEMM_W4A16_NOALLOC_MAX_M tokens and K <= QGEMM_W4A16_NOALLOC_MAX_K; anything larger is
+ * rejected with an error message (use qgemm_w4a16 then).  The function calls no cudaMalloc / cudaFree
+ * and no allocating library routine.  The first call on each device looks up the array's device
+ * address (one cudaGetSymbolAddress with that device current); make that first call outside any stream
+ * capture.  All calls on a device share the one array: it keeps the previous call's contents (the
+ * function re-zeroes the counters it needs on the given stream), and two calls that may overlap on the
+ * GPU - different streams, or different host threads - race on it and must be serialised by the caller.
+ */
+#define QGEMM_W4A16_NOALLOC_MAX_M 32
+#define QGEMM_W4A16_NOALLOC_MAX_K 16384
+#define QGEMM_W4A16_NOALLOC_SCRATCH_MB 6.3
+int qgemm_w4a16_noalloc(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group,
+                        void* C, int64_t M, int64_t N, int64_t K, int a_dtype, int out_dtype, uint32_t* status,
+                        void* stream);
+
+/*
  * int4 -> int8 unpack of a packed weight matrix into a caller-provided [N, K] int8 buffer: the
  * on-device form of torch_unpack_uint4_to_int8 (example_dequant_gemm_fine_grained.py:35-57,
  * signed_nibbles = 0) and of the vector-core unpack stage of w4a8_gemm_cv

@@ -36,6 +36,9 @@ SIGNATURES = {
     "qgemm_w4a16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p,
                                _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
                                _c.c_void_p, _c.c_void_p]),
+    "qgemm_w4a16_noalloc": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p,
+                                       _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_void_p,
+                                       _c.c_void_p]),
     "qgemm_unpack_int4": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int, _c.c_void_p]),
     "qgemm_w4a8": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64,
                               _c.c_int64, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),

@@ -448,3 +448,66 @@ int qgemm_w4a8(const int8_t* A, const uint8_t* qB, int8_t* workspace, void* C, i
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free W4A16 entry point.
+//
+// The scratch memory of the W4A16 kernels (split-K arrival counters, fp32 partial sums, the f16 copy
+// of the activations) lives here in a device array that is part of the library image, so a caller
+// never has to provide or allocate it.  Every GPU that loads the library carries this array until the
+// process exits.
+// ---------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int64_t kStaticMaxM = QGEMM_W4A16_NOALLOC_MAX_M;
+constexpr int64_t kStaticMaxK = QGEMM_W4A16_NOALLOC_MAX_K;
+constexpr int64_t kStaticMaxSms = 160;
+constexpr int64_t kStaticScratchBytes =
+    kW4CounterBytes + kStaticMaxSms * 2 * kStaticMaxM * 128 * 4 + kStaticMaxM * kStaticMaxK * 2;  // about 6.3 MB
+
+static __device__ __align__(256) unsigned char g_w4a16_static_scratch[kStaticScratchBytes];
+
+// Device address of the array above, per device.  In host code the array's name is only a handle for
+// the runtime, not a pointer a kernel could use: the real address comes from cudaGetSymbolAddress and
+// differs from GPU to GPU.
+void* g_static_scratch_addr[kMaxDevices] = {};
+std::mutex g_static_mu;
+
+int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail("device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    CUDA_OK(cudaGetSymbolAddress(&ptr, g_w4a16_static_scratch));
+    if (ptr == nullptr) return fail("cudaGetSymbolAddress returned a null address for the static scratch array");
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int qgemm_w4a16_noalloc(const void* A, const uint8_t* B_packed, const void* scales, int zero,
+                                   int64_t group, void* C, int64_t M, int64_t N, int64_t K, int a_dtype,
+                                   int out_dtype, uint32_t* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail("qgemm_w4a16_noalloc: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M, (long long)N, (long long)K);
+  if (M > kStaticMaxM || K > kStaticMaxK)
+    return fail("qgemm_w4a16_noalloc: the built-in scratch covers M <= %lld and K <= %lld (got M=%lld, K=%lld); "
+                "use qgemm_w4a16 with a caller-provided workspace for larger problems",
+                (long long)kStaticMaxM, (long long)kStaticMaxK, (long long)M, (long long)K);
+  const int64_t need = qgemm_w4a16_workspace_bytes(M, N, K);
+  if (need < 0) return -1;
+  if (need > kStaticScratchBytes)
+    return fail("qgemm_w4a16_noalloc: this problem needs %lld bytes of scratch on this device, the built-in array has %lld",
+                (long long)need, (long long)kStaticScratchBytes);
+  void* scratch = nullptr;
+  if (static_scratch_for_current_device(&scratch)) return -1;
+  // The array keeps whatever the previous call left behind.  The arrival counters must start at zero;
+  // everything else is written before it is read.
+  CUDA_OK(cudaMemsetAsync(scratch, 0, (size_t)kW4CounterBytes, static_cast<cudaStream_t>(stream)));
+  return qgemm_w4a16(A, B_packed, scales, zero, group, C, scratch, kStaticScratchBytes, M, N, K, a_dtype, out_dtype,
+                     status, stream);
+}
