@@ -5,8 +5,8 @@
 
 Headline workload (N = 1): BASELINE config[1], the W4A16 decode GEMM M=16, K=4096, N=4096, group 128,
 zero point 8, fp16.  One problem is only 8.9 MB, far below the L2 size, so a *step* is one pass over
-LAYERS = 32 distinct weight sets of that shape (285 MB > L2): 32 kernel launches, replayed from one CUDA
-graph.  `value` is algorithmic bytes (each input read once, output written once) over device time, GB/s,
+LAYERS = 32 distinct weight sets of that shape (285 MB > L2): per layer one small activation pre-pass
+and one GEMM kernel, 64 launches replayed from one CUDA graph.  `value` is algorithmic bytes (each input read once, output written once) over device time, GB/s,
 whole job over all ranks.  With N > 1 the headline config does not shard ("replicas only"): every rank
 runs its own replica (weak scaling).  The sharded configurations (config 4 by batch, config 5 by weight
 columns with an all-gather of outputs) and the other single-GPU configurations are measured in the same
@@ -32,11 +32,12 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 LAYERS = 32
+KERNELS_PER_LAYER = 2  # activation pre-pass + GEMM
 CFG2 = dict(M=16, K=4096, N=4096, group=128)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the committed ncu
-# summary under profiles/ (None until a capture exists).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# summary under profiles/.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 8847104  # profiles/w4a16_gemm_cfg2_headline.md
 
 
 def w4a16_bytes(M, K, N, group, out_bytes=2, a_bytes=2):
@@ -244,11 +245,12 @@ def run_ours(args):
                        "multi_gpu": "replicas only for this config; sharded configs are under suite"},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                         "kernel": "w4a16_gemm_kernel<16>", "us_per_launch": round(launch_us, 3),
+                         "kernel": "w4a16_gemm_kernel<16,f16> (time per layer includes its w4a16_prepare_activations pre-pass)",
+                         "us_per_launch": round(launch_us, 3),
                          "algorithmic_bytes_per_launch": w4a16_bytes(**CFG2), "peak_source": peaks_src + " (copy)"},
             "e2e": {"value": round(e2e_value, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "api": "dequant_gemm_fp16_wrapper(CPU tensors) -> CPU tensor"},
-            "gpu_launches": world * LAYERS * args.steps,
+            "gpu_launches": world * LAYERS * KERNELS_PER_LAYER * args.steps,
             "clocks": clk.summary(),
         }
         if cpu_base is not None:
@@ -311,7 +313,7 @@ def run_suite(q, world, rank, peaks):
     _, P, S = oc.make_config_inputs("cfg5", M=1)
     layers = [ColumnShardedW4A16(P, S, 8, 128).to("cuda"), ColumnShardedW4A16(P.flip(0).contiguous(), S, 8, 128).to("cuda")]
     del P
-    for M in (1, 8, 64, 512, 4096):
+    for M in (1, 8, 16, 64, 512, 4096):
         g = torch.Generator().manual_seed(M)
         A = torch.randn((M, K), generator=g).to(torch.bfloat16).cuda()
         iters = 20 if M <= 512 else 6
