@@ -1,7 +1,8 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-GEMM hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2] [--no-suite]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-suite]
+    python bench.py --case cfg5 --m 8 --launches 3      # a few launches of one configuration, for ncu
 
 Headline workload (N = 1): BASELINE config[1], the W4A16 decode GEMM M=16, K=4096, N=4096, group 128,
 zero point 8, fp16.  One problem is only 8.9 MB, far below the L2 size, so a *step* is one pass over
@@ -389,6 +390,30 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_case(args):
+    """A few eager launches of one configuration, for profilers: `--case cfg2|cfg3|cfg4|cfg5 [--m M] [--launches L]`.
+
+    Weight sets rotate so that reads stay L2-cold (cfg2: 20 sets = 160 MB; cfg5: 2 sets = 235 MB)."""
+    import tilelang_ascend_b200 as q
+    from oracle import qgemm_oracle as oc  # input generators only
+    torch.cuda.set_device(0)
+    n = args.launches
+    if args.case in ("cfg3", "cfg4", "cfg1"):
+        A, B, sa, sb = [t.cuda() for t in oc.make_config_inputs(args.case)]
+        odt = "float16" if args.case == "cfg1" else "bfloat16"
+        for _ in range(n):
+            C = q.quant_matmul(A, B, sb, scale_a=sa, out_dtype=odt)
+    else:
+        M = args.m if args.m is not None else (16 if args.case == "cfg2" else 8)
+        A, P, S = [t.cuda() for t in oc.make_config_inputs(args.case, M=M)]
+        sets = 20 if args.case == "cfg2" else 2
+        Ps = [P] + [torch.randint(0, 256, P.shape, dtype=torch.uint8, device="cuda") for _ in range(sets - 1)]
+        for i in range(n):
+            C = q.w4a16_gemm(A, Ps[i % sets], S, 8, 128)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "launches": n, "checksum": float(C.float().abs().mean())}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -397,7 +422,13 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-suite", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"], default=None,
+                    help="profiling helper: launch one configuration a few times and exit")
+    ap.add_argument("--m", type=int, default=None)
+    ap.add_argument("--launches", type=int, default=4)
     args = ap.parse_args()
+    if args.case is not None:
+        return run_case(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -291,8 +291,6 @@ int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const flo
   p.k_blocks = (int)((K + 127) / 128);
   p.status = status;
   p.wait_limit_ns = g_wait_limit_ns;
-  p.dbg_lbo = p.dbg_sbo = 0;
-  if (const char* e = getenv("QGEMM_DBG_BDESC")) sscanf(e, "%u,%u", &p.dbg_lbo, &p.dbg_sbo);
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool nk = b_layout == QGEMM_B_NK;
@@ -389,17 +387,13 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
   p.KS = (int)((K + 255) / 256);
   p.scale_rows = scale_rows;
   p.total_items = num_tiles * p.KS;
-  p.dbg = 0;
-  if (const char* e = getenv("QGEMM_DBG_W4")) p.dbg = atoi(e);
-  p.trace = nullptr;
-  if (const char* e = getenv("QGEMM_TRACE_PTR")) p.trace = reinterpret_cast<unsigned long long*>(strtoull(e, nullptr, 0));
   p.status = status;
   p.wait_limit_ns = g_wait_limit_ns;
   int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
   if (p.total_items < grid) grid = p.total_items;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf = out_dtype == QGEMM_DT_BF16;
-  if (!(p.dbg & 32)) {
+  {
     const long long n_chunks = (long long)M * K / 8;
     const long long blocks = (n_chunks + 255) / 256;
     if (blocks > 0x7fffffffll) return fail("qgemm_w4a16: activation tensor too large");

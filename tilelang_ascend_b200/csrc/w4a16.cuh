@@ -44,17 +44,7 @@ struct W4A16Params {
   long long total_items;
   uint32_t* status;
   unsigned long long wait_limit_ns;
-  int dbg;  // bring-up only: bit 0 skips the dequant arithmetic, bit 1 skips the MMA issue
-  unsigned long long* trace;  // bring-up only: per-item cycle stamps of CTA 0 (8 events per item), nullable
 };
-
-__device__ __forceinline__ void w4_trace(const W4A16Params& p, int item, int ev) {
-  if (p.trace != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && item < 256) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
-    p.trace[item * 8 + ev] = t;
-  }
-}
 
 constexpr int W4_BN = 128;        // weight rows per tile
 constexpr int W4_SLAB_K = 256;    // K per pipeline item: 128 packed bytes per row
@@ -74,11 +64,7 @@ struct W4Cfg {
   static constexpr int W_STAGES = (MT <= 64) ? 3 : 2;
   static constexpr int A_KB_BYTES = MT * 128;          // one 64-wide K block of activations
   static constexpr int A_BYTES = 4 * A_KB_BYTES;       // one 256-wide slab
-  // Consecutive K steps accumulate round-robin into NACC independent accumulators (summed in the
-  // epilogue): with few tokens one MMA is far shorter than its accumulate latency, and a single
-  // accumulator would serialise the whole chain.
-  static constexpr int NACC = 1;
-  static constexpr int ACC_COLS = 2 * NACC * MT;       // two buffers of NACC accumulators
+  static constexpr int ACC_COLS = 2 * MT;              // two accumulator buffers
   static constexpr int TMEM_COLS = 512;
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_BYTES = RAW_STAGES * W4_RAW_BYTES + A_STAGES * A_BYTES + BAR_BYTES + 1024;
@@ -228,7 +214,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_w = tmem_base + Cfg::ACC_COLS;  // ring of dequantised-weight columns
-  const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns, (uint32_t)(p.dbg >> 8)};
+  const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns, 0};
 
   const int G = gridDim.x;
   const int cta = blockIdx.x;
@@ -243,21 +229,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
       bool ok = true;
       const uint32_t tx = W4_RAW_PACKED + (p.has_scales ? p.scale_rows * 256 : 0);
-      const int pf = (p.dbg >> 16) & 0xff;  // L2 prefetch distance in slabs
-      int titem = 0;
       while (ok && seg.next(tile, ks0, ks1)) {
         const int n0 = (tile / p.m_tiles) * W4_BN;
         for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(&raw_empty[rs], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           uint8_t* dst = raw_base + rs * W4_RAW_BYTES;
-          // Run ahead of the shared-memory ring in L2: ask for the slab `pf` items further on (same tile
-          // row block if it exists, else the next tile's first slabs; coordinates past the tensor are harmless).
-          if (pf > 0) {
-            const int ksp = ks + pf;
-            if (ksp < p.KS) tma_prefetch_l2_2d(&tmW, ksp * (W4_SLAB_K / 2), n0);
-            else if (tile + 1 < p.num_tiles)
-              tma_prefetch_l2_2d(&tmW, (ksp - p.KS) * (W4_SLAB_K / 2), ((tile + 1) / p.m_tiles) * W4_BN);
-          }
           mbar_arrive_expect_tx(&raw_full[rs], tx);
           tma_load_2d(dst, &tmW, &raw_full[rs], ks * (W4_SLAB_K / 2), n0);
           if (p.has_scales) {
@@ -266,7 +242,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           }
           issued_mask |= 1u << rs;
           parity_mask = (parity_mask & ~(1u << rs)) | (phase << rs);
-          w4_trace(p, titem++, 0);
           if (++rs == RS) { rs = 0; phase ^= 1u; }
         }
       }
@@ -327,35 +302,29 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const uint32_t a_base_u32 = smem_u32(a_base);
       int ws = 0, as = 0;
       uint32_t wphase = 0, aphase = 0;
-      int it = 0, titem = 0;
+      int it = 0;
       bool ok = true;
       while (ok && seg.next(tile, ks0, ks1)) {
         const int buf = it & 1;
         const uint32_t tphase = (it >> 1) & 1;
         if (!mbar_wait_warp(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t d = tmem_base + buf * (Cfg::NACC * MT);
-        uint32_t started = 0;  // bit a set once accumulator a has been written in this segment
+        const uint32_t d = tmem_base + buf * MT;
+        uint32_t started = 0;  // 0 for the first MMA of the segment: overwrite the accumulator
         for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait_warp(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
           if (!mbar_wait_warp(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
           tc_fence_after_sync();
-          w4_trace(p, titem, 5);
           const uint64_t adesc0 = desc_hi | (uint64_t)(((a_base_u32 + as * Cfg::A_BYTES) & 0x3FFFFu) >> 4);
           const uint32_t tW = tmem_w + ws * W4_W_COLS;
-          if (!(p.dbg & 2)) {
 #pragma unroll
-            for (int kk = 0; kk < W4_SLAB_K / 16; ++kk) {  // 16 k per MMA: 8 TMEM columns, 32 bytes of smem
-              constexpr int NA = Cfg::NACC;
-              const int a = kk & (NA - 1);
-              const uint32_t off = (uint32_t)(((kk >> 2) * Cfg::A_KB_BYTES + (kk & 3) * 32) >> 4);
-              umma_f16_ts_elect(leader, d + a * MT, tW + kk * 8, adesc0 + off, idesc, (started >> a) & 1u);
-              started |= 1u << a;
-            }
+          for (int kk = 0; kk < W4_SLAB_K / 16; ++kk) {  // 16 k per MMA: 8 TMEM columns, 32 bytes of smem
+            const uint32_t off = (uint32_t)(((kk >> 2) * Cfg::A_KB_BYTES + (kk & 3) * 32) >> 4);
+            umma_f16_ts_elect(leader, d, tW + kk * 8, adesc0 + off, idesc, started);
+            started = 1u;
           }
           umma_commit_elect(leader, &w_empty[ws]);
           umma_commit_elect(leader, &a_empty[as]);
-          w4_trace(p, titem++, 6);
           if (++ws == WS) { ws = 0; wphase ^= 1u; }
           if (++as == AS) { as = 0; aphase ^= 1u; }
         }
@@ -388,22 +357,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const bool ok = mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE);
       if (ok) {
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (Cfg::NACC * MT);
-        constexpr int nacc = Cfg::NACC;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * MT;
 #pragma unroll 1
         for (int c = 0; c < MT / CH; ++c) {
           uint32_t r[CH];
           if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + c * CH, r);
           else tmem_ld_32x32b_x32(taddr + c * CH, r);
           tmem_ld_wait();
-          for (int a = 1; a < nacc; ++a) {
-            uint32_t r2[CH];
-            if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + a * MT + c * CH, r2);
-            else tmem_ld_32x32b_x32(taddr + a * MT + c * CH, r2);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
-          }
           if (full_tile) {
             if (n < p.N) {
 #pragma unroll
@@ -503,15 +463,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int srow0 = (p.group <= W4_SLAB_K) ? (64 * j) / p.group : 0;
     const int srow1 = (p.group <= W4_SLAB_K) ? (64 * j + 32) / p.group : 0;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    int rs = 0, ws = 0, titem = 0;
+    int rs = 0, ws = 0;
     uint32_t rphase = 0, wphase = 0;
     bool ok = true;
-    const bool tr_first = (wd == 0), tr_last = (wd == W4_DQ_WARPS - 1);
     while (ok && seg.next(tile, ks0, ks1)) {
       for (int ks = ks0; ks < ks1; ++ks) {
         if (!mbar_wait_warp(&raw_full[rs], rphase, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
-        if (tr_first) w4_trace(p, titem, 1);
-        if (tr_last) w4_trace(p, titem, 7);
         const uint8_t* rawp = raw_base + rs * W4_RAW_BYTES;
         const uint4 v0 = *reinterpret_cast<const uint4*>(rawp + off0);
         const uint4 v1 = *reinterpret_cast<const uint4*>(rawp + off1);
@@ -522,10 +479,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
           s21 = (uint32_t)__half_as_ushort(sS[srow1 * W4_BN + row]) * 0x00010001u;
         }
         uint32_t o[32];
-        if (p.dbg & 1) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = v0.x + i;
-        } else {
         w4_dequant8(v0.x, sub_lo, sub_hi, s20, scaled, o + 0);
         w4_dequant8(v0.y, sub_lo, sub_hi, s20, scaled, o + 4);
         w4_dequant8(v0.z, sub_lo, sub_hi, s20, scaled, o + 8);
@@ -534,23 +487,16 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         w4_dequant8(v1.y, sub_lo, sub_hi, s21, scaled, o + 20);
         w4_dequant8(v1.z, sub_lo, sub_hi, s21, scaled, o + 24);
         w4_dequant8(v1.w, sub_lo, sub_hi, s21, scaled, o + 28);
-        }
         // the packed bytes are in registers: hand the raw stage back to the producer
         __syncwarp();
         if (lane == 0) mbar_arrive(&raw_empty[rs]);
         if (++rs == RS) { rs = 0; rphase ^= 1u; }
-        if (tr_first) w4_trace(p, titem, 2);
 
         if (!mbar_wait_warp(&w_empty[ws], wphase ^ 1u, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
         tc_fence_after_sync();
-        if (tr_first) w4_trace(p, titem, 3);
-        if (!(p.dbg & 16)) {
-          tmem_st_32x32b_x32(tmem_w + lane_addr + ws * W4_W_COLS + j * 32, o);
-          tmem_st_wait();
-        }
+        tmem_st_32x32b_x32(tmem_w + lane_addr + ws * W4_W_COLS + j * 32, o);
+        tmem_st_wait();
         tc_fence_before_sync();
-        if (tr_first) w4_trace(p, titem, 4);
-        ++titem;
         __syncwarp();
         if (lane == 0) mbar_arrive(&w_full[ws]);
         if (++ws == WS) { ws = 0; wphase ^= 1u; }

@@ -24,7 +24,6 @@ struct W8A8Params {
   int m_tiles, n_tiles, num_tiles, k_blocks;
   uint32_t* status;  // nullable device word
   unsigned long long wait_limit_ns;
-  uint32_t dbg_lbo, dbg_sbo;  // bring-up only: non-zero overrides of the MN-major B descriptor offsets
 };
 
 constexpr int W8_BM = 128;      // tile rows (= MMA M, one TMEM lane per row)
@@ -173,8 +172,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               bdesc = make_desc_kmajor(sB) + (uint64_t)((k * W8_UMMA_K) >> 4);
             } else {
               // [K rows][128 B of N]: 32 K rows per MMA = 4096 B; the next 128 columns are one box (16 KB) further.
-              bdesc = make_smem_desc_sw128(sB + k * (W8_UMMA_K * 128), p.dbg_lbo ? p.dbg_lbo : W8_BK * 128,
-                                           p.dbg_sbo ? p.dbg_sbo : 1024);
+              bdesc = make_desc_mnmajor(sB + k * (W8_UMMA_K * 128), W8_BK * 128);
             }
             umma_i8_ss(d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
