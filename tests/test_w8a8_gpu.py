@@ -64,6 +64,8 @@ SHAPES = [
     (2, 256, 2048, 1024),
     (0, 1024, 1024, 1024),
     (8, 1024, 1024, 1024),  # the reference example's default case (example_quant_batch_matmul.py:120-133)
+    (20, 300, 272, 528),    # enough 256 x 256 tiles for the two-CTA kernel, ragged in M, N and K
+    (0, 2304, 528, 2320),
 ]
 
 
@@ -78,7 +80,7 @@ def test_accumulators_and_output_exact(batch, M, K, N, odt):
     _cmp(C, ref)
 
 
-@pytest.mark.parametrize("batch,M,K,N", [(0, 96, 160, 144), (2, 130, 512, 272), (0, 512, 4096, 256)])
+@pytest.mark.parametrize("batch,M,K,N", [(0, 96, 160, 144), (2, 130, 512, 272), (0, 512, 4096, 256), (24, 260, 144, 528)])
 def test_nk_layout_and_int32_output(batch, M, K, N):
     q = _q()
     A, B, sa, sb = oc.make_w8a8_inputs(batch, M, K, N, seed=5)
@@ -162,6 +164,31 @@ def test_config3_full_size_properties():
     acc1 = q.quant_matmul(A1.cuda(), Bd, None, out_dtype=torch.int32)
     acc2 = q.quant_matmul(A2.cuda(), Bd, None, out_dtype=torch.int32)
     assert torch.equal(acc1 + acc2, acc)
+
+
+def test_two_cta_kernel_variant():
+    """The cta_group::2 form of the kernel (256 x 256 tile per CTA pair) is opt-in through QGEMM_W8_PAIR=1,
+    read once per process, so it is exercised in a child process: ragged M/N/K, both layouts, bit-exact."""
+    import os
+    import subprocess
+    import sys
+    code = r"""
+import torch
+from oracle import qgemm_oracle as oc
+import tilelang_ascend_b200 as q
+for batch, M, K, N in [(20, 300, 272, 528), (0, 2304, 528, 2320), (8, 1024, 1024, 1024)]:
+    A, B, sa, sb = oc.make_w8a8_inputs(batch, M, K, N, seed=M)
+    ref, acc_ref = oc.quant_matmul_ref(A, B, sb, "bfloat16", scale_a=sa, return_acc=True)
+    C, acc = q.quant_matmul(A.cuda(), B.cuda(), sb.cuda(), scale_a=sa.cuda(), out_dtype="bfloat16", return_accumulators=True)
+    assert torch.equal(acc.cpu(), acc_ref) and torch.equal(C.cpu(), ref), (batch, M, K, N)
+    acc2 = q.quant_matmul(A.cuda(), B.transpose(-1, -2).contiguous().cuda(), None, out_dtype=torch.int32, b_layout="NK")
+    assert torch.equal(acc2.cpu(), acc_ref), ("NK", batch, M, K, N)
+print("pair ok")
+"""
+    env = dict(os.environ, QGEMM_W8_PAIR="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "pair ok" in r.stdout, r.stdout + r.stderr
 
 
 def test_rejects_bad_arguments():

@@ -22,6 +22,7 @@ struct W8A8Params {
   int sb_mode;  // 0: one value for all; 1: [N]; 2: [batch, N]
   int sa_mode;  // 0: none; 1: [M]; 2: [batch, M]
   int m_tiles, n_tiles, num_tiles, k_blocks;
+  int bn;            // columns per tile actually computed: a multiple of 32, at most the kernel's BN
   uint32_t* status;  // nullable device word
   unsigned long long wait_limit_ns;
 };
@@ -111,7 +112,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         int b, m_blk, n_blk;
         w8_decode_tile(p, tile, b, m_blk, n_blk);
-        const int m0 = m_blk * W8_BM, n0 = n_blk * BN;
+        const int m0 = m_blk * W8_BM, n0 = n_blk * p.bn;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           uint8_t* sA = smem + stage * Cfg::STAGE_BYTES;
@@ -147,7 +148,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, B_NK ? 0 : 1, W8_BM, BN);
+      const uint32_t idesc = make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, B_NK ? 0 : 1, W8_BM, (uint32_t)p.bn);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -207,12 +208,13 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const float* sbp = p.scale_b + (p.sb_mode == 2 ? (size_t)b * p.N : 0);
       const size_t row_off = ((size_t)b * p.M + (row_ok ? m : 0)) * (size_t)p.N;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+      const int chunks = p.bn >> 5;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < chunks; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
-        const int n = n_blk * BN + c * 32;
+        const int n = n_blk * p.bn + c * 32;
         if (row_ok && n < p.N) {
           if (p.acc_out != nullptr) {
             int4* dst = reinterpret_cast<int4*>(p.acc_out + row_off + n);
@@ -255,6 +257,234 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Two-CTA form: a pair of CTAs (a cluster of 2 on neighbouring SMs) computes one 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and one half (128 columns) of B, so the
+// bytes pulled from L2 per MMA cycle drop by a third compared with the one-CTA 128 x 256 tile, which is what
+// limits that kernel.  Each load goes into the loading CTA's own shared memory; only the completion count
+// lives in the leader's barrier.  The leader CTA (rank 0) issues the MMAs; stage-free and accumulator-ready
+// signals are committed to the barrier of each CTA separately.
+// ---------------------------------------------------------------------------------------------------
+constexpr int W8P_BN = 256;
+constexpr int W8P_STAGES = 6;
+constexpr int W8P_A_BYTES = W8_BM * W8_BK;        // 16 KB: this CTA's 128 rows
+constexpr int W8P_B_BYTES = 128 * W8_BK;          // 16 KB: this CTA's 128 columns of B
+constexpr int W8P_STAGE_BYTES = W8P_A_BYTES + W8P_B_BYTES;
+constexpr int W8P_SMEM_BYTES = W8P_STAGES * W8P_STAGE_BYTES + 256 + 1024;
+constexpr int W8P_GROUP_M = 4;
+
+__device__ __forceinline__ void w8p_decode_tile(const W8A8Params& p, int m2_tiles, int tile, int& b, int& m_blk, int& n_blk) {
+  const int per_batch = m2_tiles * p.n_tiles;
+  b = tile / per_batch;
+  const int r = tile - b * per_batch;
+  const int band = W8P_GROUP_M * p.n_tiles;
+  const int g = r / band;
+  const int first_m = g * W8P_GROUP_M;
+  const int gsz = min(m2_tiles - first_m, W8P_GROUP_M);
+  const int in_band = r - g * band;
+  m_blk = first_m + in_band % gsz;
+  n_blk = in_band / gsz;
+}
+
+// p.m_tiles counts 256-row tiles here; p.num_tiles = batch * m_tiles * n_tiles (n_tiles of 256 columns).
+template <bool B_NK, bool OUT_BF16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W8_THREADS, 1)
+w8a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const W8A8Params p) {
+  constexpr int STAGES = W8P_STAGES;
+  constexpr int BN = W8P_BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * W8P_STAGE_BYTES);
+  uint64_t* full = bars;                 // used in the leader CTA only
+  uint64_t* empty = bars + STAGES;       // one set per CTA
+  uint64_t* tfull = bars + 2 * STAGES;   // one set per CTA
+  uint64_t* tempty = tfull + 2;          // used in the leader CTA only (8 arrivals: 4 epilogue warps x 2 CTAs)
+  uint64_t* drain = tempty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 8);
+    }
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns, 0};
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < p.num_tiles; tile += n_pairs) {
+        int b, m_blk, n_blk;
+        w8p_decode_tile(p, p.m_tiles, tile, b, m_blk, n_blk);
+        const int m0 = m_blk * 256 + (int)rank * 128;
+        const int nh = n_blk * BN + (int)rank * 128;  // this CTA's half of the tile's columns
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* sA = smem + stage * W8P_STAGE_BYTES;
+          uint8_t* sB = sA + W8P_A_BYTES;
+          const uint32_t full_leader = mapa_u32(smem_u32(&full[stage]), 0);
+          if (leader) mbar_arrive_expect_tx(&full[stage], 2 * W8P_STAGE_BYTES);
+          tma_load_3d_pair(sA, &tmA, full_leader, kb * W8_BK, m0, b);
+          if constexpr (B_NK) tma_load_3d_pair(sB, &tmB, full_leader, kb * W8_BK, nh, b);
+          else tma_load_3d_pair(sB, &tmB, full_leader, nh, kb * W8_BK, b);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Gave up: the completion counts of this CTA's copies live in the leader, so simply leave the
+        // copies already issued a bounded time to land before the CTA may exit.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 100000ull) {}
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, B_NK ? 0 : 1, 256, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < p.num_tiles; tile += n_pairs, ++it) {
+        const int buf = it & 1;
+        const uint32_t tphase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sA = smem_u32(smem + stage * W8P_STAGE_BYTES);
+          const uint32_t sB = sA + W8P_A_BYTES;
+          const uint64_t a0 = make_desc_kmajor(sA);
+#pragma unroll
+          for (int k = 0; k < W8_BK / W8_UMMA_K; ++k) {
+            const uint64_t adesc = a0 + (uint64_t)((k * W8_UMMA_K) >> 4);
+            uint64_t bdesc;
+            if constexpr (B_NK) bdesc = make_desc_kmajor(sB) + (uint64_t)((k * W8_UMMA_K) >> 4);
+            else bdesc = make_desc_mnmajor(sB + k * (W8_UMMA_K * 128), W8_BK * 128);
+            umma_i8_ss_pair(d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          const uint32_t e_local = smem_u32(&empty[stage]);
+          umma_commit_pair(e_local);
+          umma_commit_pair(mapa_u32(e_local, 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) {
+          const uint32_t t_local = smem_u32(&tfull[buf]);
+          umma_commit_pair(t_local);
+          umma_commit_pair(mapa_u32(t_local, 1));
+        }
+      }
+      if (!ok) {
+        umma_commit_pair(smem_u32(drain));
+        const uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(drain, 0)) {
+          if (global_timer_ns() - t0 > p.wait_limit_ns) break;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    int it = 0;
+    for (int tile = pair; tile < p.num_tiles; tile += n_pairs, ++it) {
+      int b, m_blk, n_blk;
+      w8p_decode_tile(p, p.m_tiles, tile, b, m_blk, n_blk);
+      const int buf = it & 1;
+      const uint32_t tphase = (it >> 1) & 1;
+      if (!mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after_sync();
+      const int m = m_blk * 256 + (int)rank * 128 + q * 32 + lane;
+      const bool row_ok = m < p.M;
+      float sa = 1.0f;
+      if (p.sa_mode != 0 && row_ok) sa = __ldg(p.scale_a + (p.sa_mode == 2 ? (size_t)b * p.M : 0) + m);
+      const float* sbp = p.scale_b + (p.sb_mode == 2 ? (size_t)b * p.N : 0);
+      const size_t row_off = ((size_t)b * p.M + (row_ok ? m : 0)) * (size_t)p.N;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int n = n_blk * BN + c * 32;
+        if (row_ok && n < p.N) {
+          if (p.acc_out != nullptr) {
+            int4* dst = reinterpret_cast<int4*>(p.acc_out + row_off + n);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (n + 4 * j < p.N) dst[j] = make_int4((int)r[4 * j], (int)r[4 * j + 1], (int)r[4 * j + 2], (int)r[4 * j + 3]);
+          }
+          uint16_t* cbase = reinterpret_cast<uint16_t*>(p.C) + row_off + n;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (p.C != nullptr && n + 8 * j < p.N) {
+              uint32_t o[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int col = 8 * j + 2 * e;
+                float s0, s1;
+                if (p.sb_mode == 0) { s0 = s1 = __ldg(sbp); }
+                else { s0 = __ldg(sbp + n + col); s1 = __ldg(sbp + n + col + 1); }
+                float f0 = __int2float_rn((int)r[col]);
+                float f1 = __int2float_rn((int)r[col + 1]);
+                if (p.sa_mode != 0) { f0 = __fmul_rn(f0, sa); f1 = __fmul_rn(f1, sa); }
+                f0 = __fmul_rn(f0, s0);
+                f1 = __fmul_rn(f1, s1);
+                o[e] = pack_out2<OUT_BF16>(f0, f1);
+              }
+              *reinterpret_cast<uint4*>(cbase + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[buf]), 0));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // nothing may still be signalling into a CTA that has left
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
