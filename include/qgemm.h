@@ -109,6 +109,19 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
                 int out_dtype, uint32_t* status, void* stream);
 
 /*
+ * Batched W4A16: `batch` independent problems of one shape in a single launch (for example the experts of
+ * a mixture layer, or several projections applied to their own activations), the W4A16 analogue of the
+ * batch dimension of simple_quant_batch_matmul (examples/quant_batch_matmul/example_quant_batch_matmul.py:38-41).
+ * A: [batch, M, K]; B_packed: [batch, N, K/2]; scales: nullable [batch, K/group, N]; C: [batch, M, N];
+ * everything else as qgemm_w4a16, which is the batch = 1 case.  All (problem, tile, K slab) work items
+ * are dealt to the persistent CTAs together, so small problems do not pay one launch each.
+ */
+int64_t qgemm_w4a16_batched_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K);
+int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
+                        void* workspace, int64_t workspace_bytes, int64_t batch, int64_t M, int64_t N, int64_t K,
+                        int a_dtype, int out_dtype, uint32_t* status, void* stream);
+
+/*
  * W4A16 dequantize-GEMM that needs no memory from the caller beyond inputs and output.  (No counterpart
  * in the reference: there the wrapper allocates every workspace with torch before the call.)
  *

@@ -120,6 +120,28 @@ def test_split_k_is_deterministic_and_counters_stay_clean():
         assert torch.equal(o, outs[0])
 
 
+@pytest.mark.parametrize("batch,M,K,N,dt", [(3, 5, 512, 264, "float16"), (4, 16, 1024, 256, "bfloat16"),
+                                             (2, 70, 256, 384, "float16"), (6, 1, 2048, 128, "bfloat16")])
+def test_batched_matches_oracle_and_single_calls(batch, M, K, N, dt):
+    """Independent problems of one shape in one launch: every batch entry must match the oracle and the
+    same problem launched on its own (identical arithmetic per element, possibly another fp32 split order)."""
+    q = _q()
+    ins = [oc.make_w4a16_inputs(M, K, N, dt, 128, seed=100 + b) for b in range(batch)]
+    A = torch.stack([i[0] for i in ins]).cuda()
+    P = torch.stack([i[1] for i in ins]).cuda()
+    S = torch.stack([i[2] for i in ins]).cuda()
+    C = q.w4a16_gemm(A, P, S, 8, 128)
+    assert C.shape == (batch, M, N)
+    for b in range(batch):
+        ref = oc.dequant_gemm_fp16_ref(ins[b][0], ins[b][1], dt, ins[b][2], 8, 128)
+        _close(C[b], ref)
+        single = q.w4a16_gemm(A[b].contiguous(), P[b].contiguous(), S[b].contiguous(), 8, 128)
+        torch.testing.assert_close(C[b].float(), single.float(), rtol=2e-3, atol=2e-3)
+    C2 = q.w4a16_gemm(A, P, None)  # unscaled, batched
+    for b in range(batch):
+        _close(C2[b], oc.dequant_gemm_fp16_ref(ins[b][0], ins[b][1], dt))
+
+
 @pytest.mark.parametrize("M", [1, 8, 64])
 def test_config5_decode_full_size(M):
     """BASELINE config 5 decode shapes at full size (K = 8192, N = 28672, bf16): a band of output columns

@@ -36,6 +36,10 @@ SIGNATURES = {
     "qgemm_w4a16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p,
                                _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
                                _c.c_void_p, _c.c_void_p]),
+    "qgemm_w4a16_batched_workspace_bytes": (_c.c_int64, [_c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64]),
+    "qgemm_w4a16_batched": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p,
+                                       _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
+                                       _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
     "qgemm_w4a16_noalloc": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p,
                                        _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_void_p,
                                        _c.c_void_p]),

@@ -338,7 +338,7 @@ int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const flo
 
 int64_t qgemm_w4a16_counter_bytes(void) { return kW4CounterBytes; }
 
-int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+int64_t qgemm_w4a16_batched_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K) {
   (void)N;
   int sms = 0;
   if (ensure_device(&sms)) return -1;
@@ -346,12 +346,24 @@ int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const int mt = w4_pick_mt(M);
   // the arrival counters first (fixed place whatever the tile height), then two partial slots of
   // [MT][128] fp32 per CTA, then the f16 copy of the activations in the kernel's K order
-  return kW4CounterBytes + grid * 2 * (int64_t)mt * 128 * 4 + M * K * 2;
+  return kW4CounterBytes + grid * 2 * (int64_t)mt * 128 * 4 + batch * M * K * 2;
+}
+
+int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  return qgemm_w4a16_batched_workspace_bytes(1, M, N, K);
 }
 
 int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
                 void* workspace, int64_t workspace_bytes, int64_t M, int64_t N, int64_t K, int a_dtype,
                 int out_dtype, uint32_t* status, void* stream) {
+  return qgemm_w4a16_batched(A, B_packed, scales, zero, group, C, workspace, workspace_bytes, 1, M, N, K, a_dtype,
+                             out_dtype, status, stream);
+}
+
+int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
+                        void* workspace, int64_t workspace_bytes, int64_t batch, int64_t M, int64_t N, int64_t K,
+                        int a_dtype, int out_dtype, uint32_t* status, void* stream) {
+  if (batch <= 0 || batch > 65535) return fail("qgemm_w4a16: batch must be in 1..65535 (got %lld)", (long long)batch);
   if (M <= 0 || N <= 0 || K <= 0) return fail("qgemm_w4a16: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M, (long long)N, (long long)K);
   if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return fail("qgemm_w4a16: dimension too large");
   if (A == nullptr || B_packed == nullptr || C == nullptr) return fail("qgemm_w4a16: A, B_packed and C must not be null");
@@ -369,7 +381,7 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
     zero = 0;
     group = K;
   }
-  const int64_t need = qgemm_w4a16_workspace_bytes(M, N, K);
+  const int64_t need = qgemm_w4a16_batched_workspace_bytes(batch, M, N, K);
   if (need < 0) return -1;
   if (workspace == nullptr || workspace_bytes < need) return fail("qgemm_w4a16: workspace of %lld bytes needed (got %lld)", (long long)need, (long long)workspace_bytes);
 
@@ -380,26 +392,26 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
   CUtensorMap tmW, tmS, tmA;
   memset(&tmS, 0, sizeof(tmS));
   {
-    const uint64_t dims[2] = {(uint64_t)(K / 2), (uint64_t)N};
-    const uint64_t str[1] = {(uint64_t)(K / 2)};
-    const uint32_t box[2] = {128, 128};
-    if (encode_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, B_packed, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    const uint64_t dims[3] = {(uint64_t)(K / 2), (uint64_t)N, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)(K / 2), (uint64_t)N * (uint64_t)(K / 2)};
+    const uint32_t box[3] = {128, 128, 1};
+    if (encode_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B_packed, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
   }
   int scale_rows = 1;
   if (scales != nullptr) {
     scale_rows = group < 256 ? (int)(256 / group) : 1;
-    const uint64_t dims[2] = {(uint64_t)N, (uint64_t)(K / group)};
-    const uint64_t str[1] = {(uint64_t)N * 2};
-    const uint32_t box[2] = {128, (uint32_t)scale_rows};
-    if (encode_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+    const uint64_t dims[3] = {(uint64_t)N, (uint64_t)(K / group), (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)N * 2, (uint64_t)(K / group) * (uint64_t)N * 2};
+    const uint32_t box[3] = {128, (uint32_t)scale_rows, 1};
+    if (encode_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
   }
   const int64_t grid_max = sms < kW4MaxGrid ? sms : kW4MaxGrid;
   uint8_t* a_prepared = static_cast<uint8_t*>(workspace) + kW4CounterBytes + grid_max * 2 * (int64_t)mt * 128 * 4;
   {
-    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
-    const uint64_t str[1] = {(uint64_t)K * 2};
-    const uint32_t box[2] = {64, (uint32_t)mt};
-    if (encode_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a_prepared, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)M * (uint64_t)K * 2};
+    const uint32_t box[3] = {64, (uint32_t)mt, 1};
+    if (encode_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, a_prepared, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
   }
 
   qg::W4A16Params p;
@@ -414,7 +426,8 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
   p.has_scales = scales != nullptr;
   p.m_tiles = (int)((M + mt - 1) / mt);
   p.n_tiles = (int)((N + 127) / 128);
-  const int64_t num_tiles = (int64_t)p.m_tiles * p.n_tiles;
+  p.batch = (int)batch;
+  const int64_t num_tiles = batch * (int64_t)p.m_tiles * p.n_tiles;
   if (num_tiles > 0x3fffffff) return fail("qgemm_w4a16: too many tiles");
   p.num_tiles = (int)num_tiles;
   p.KS = (int)((K + 255) / 256);
@@ -427,7 +440,7 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf = out_dtype == QGEMM_DT_BF16;
   {
-    const long long n_chunks = (long long)M * K / 8;
+    const long long n_chunks = (long long)batch * M * K / 8;
     const long long blocks = (n_chunks + 255) / 256;
     if (blocks > 0x7fffffffll) return fail("qgemm_w4a16: activation tensor too large");
     qg::w4a16_prepare_activations<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint4*>(A),

@@ -38,7 +38,8 @@ struct W4A16Params {
   int group;            // quantisation group size along K
   int zero;             // integer zero point (0..15)
   int has_scales;       // 0: weights are the raw nibble values (scale 1)
-  int m_tiles, n_tiles, num_tiles;
+  int batch;            // independent problems of the same shape (A, B_packed, scales, C all carry a leading batch dimension)
+  int m_tiles, n_tiles, num_tiles;  // num_tiles = batch * n_tiles * m_tiles; tile = (b * n_tiles + n_tile) * m_tiles + m_tile
   int KS;               // 256-wide K slabs per tile
   int scale_rows;       // scale rows fetched per slab (256 / group, at least 1)
   long long total_items;
@@ -76,6 +77,15 @@ struct W4Cfg {
 __device__ __forceinline__ long long w4_range_begin(long long T, int G, int b) { return T * b / G; }
 // The CTA whose range holds item i.
 __device__ __forceinline__ int w4_owner(long long T, int G, long long i) { return (int)(((i + 1) * G - 1) / T); }
+
+// tile -> batch index, first weight row, first token
+__device__ __forceinline__ void w4_tile_coords(const W4A16Params& p, int tile, int mt, int& b, int& n0, int& m0) {
+  const int per_batch = p.n_tiles * p.m_tiles;
+  b = tile / per_batch;
+  const int t = tile - b * per_batch;
+  n0 = (t / p.m_tiles) * 128;
+  m0 = (t % p.m_tiles) * mt;
+}
 
 struct W4SegIter {
   long long item, end;
@@ -230,15 +240,16 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       bool ok = true;
       const uint32_t tx = W4_RAW_PACKED + (p.has_scales ? p.scale_rows * 256 : 0);
       while (ok && seg.next(tile, ks0, ks1)) {
-        const int n0 = (tile / p.m_tiles) * W4_BN;
+        int b, n0, m0;
+        w4_tile_coords(p, tile, MT, b, n0, m0);
         for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(&raw_empty[rs], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           uint8_t* dst = raw_base + rs * W4_RAW_BYTES;
           mbar_arrive_expect_tx(&raw_full[rs], tx);
-          tma_load_2d(dst, &tmW, &raw_full[rs], ks * (W4_SLAB_K / 2), n0);
+          tma_load_3d(dst, &tmW, &raw_full[rs], ks * (W4_SLAB_K / 2), n0, b);
           if (p.has_scales) {
             const int srow = (p.group <= W4_SLAB_K) ? ks * p.scale_rows : (ks * W4_SLAB_K) / p.group;
-            tma_load_2d(dst + W4_RAW_PACKED, &tmS, &raw_full[rs], n0, srow);
+            tma_load_3d(dst + W4_RAW_PACKED, &tmS, &raw_full[rs], n0, srow, b);
           }
           issued_mask |= 1u << rs;
           parity_mask = (parity_mask & ~(1u << rs)) | (phase << rs);
@@ -265,14 +276,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
       bool ok = true;
       while (ok && seg.next(tile, ks0, ks1)) {
-        const int m0 = (tile % p.m_tiles) * MT;
+        int b, n0, m0;
+        w4_tile_coords(p, tile, MT, b, n0, m0);
         for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(&a_empty[as], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           uint8_t* dstA = a_base + as * Cfg::A_BYTES;
           mbar_arrive_expect_tx(&a_full[as], Cfg::A_BYTES);
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb)
-            tma_load_2d(dstA + kb * Cfg::A_KB_BYTES, &tmA, &a_full[as], ks * W4_SLAB_K + kb * 64, m0);
+            tma_load_3d(dstA + kb * Cfg::A_KB_BYTES, &tmA, &a_full[as], ks * W4_SLAB_K + kb * 64, m0, b);
           issued_mask |= 1u << as;
           parity_mask = (parity_mask & ~(1u << as)) | (phase << as);
           if (++as == AS) { as = 0; phase ^= 1u; }
@@ -344,14 +356,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     constexpr int CH = Cfg::CH;
     const int q = warp & 3;
     const int nl = q * 32 + lane;  // weight row inside the tile == TMEM lane
-    uint16_t* Cout = reinterpret_cast<uint16_t*>(p.C);
     int it = 0;
     while (seg.next(tile, ks0, ks1)) {
       const int buf = it & 1;
       const uint32_t tphase = (it >> 1) & 1;
       ++it;
-      const int n = (tile / p.m_tiles) * W4_BN + nl;
-      const int m0 = (tile % p.m_tiles) * MT;
+      int b, n0, m0;
+      w4_tile_coords(p, tile, MT, b, n0, m0);
+      const int n = n0 + nl;
+      uint16_t* Cout = reinterpret_cast<uint16_t*>(p.C) + (size_t)b * p.M * p.N;
       const bool full_tile = (ks0 == 0 && ks1 == p.KS);
       const int my_slot = (ks1 < p.KS) ? 2 * cta + 1 : 2 * cta;
       const bool ok = mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE);

@@ -117,20 +117,20 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       bool ok = true;
       const uint32_t tx = W4_RAW_PACKED + (SCALED ? p.scale_rows * 256 : 0) + 4 * Cfg::A_KB_BYTES;
       while (ok && seg.next(tile, ks0, ks1)) {
-        const int n0 = (tile / p.m_tiles) * W4_BN;
-        const int m0 = (tile % p.m_tiles) * MT;
+        int b, n0, m0;
+        w4_tile_coords(p, tile, MT, b, n0, m0);
         for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(&empty[s], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           uint8_t* dst = smem + s * Cfg::STAGE_BYTES;
           mbar_arrive_expect_tx(&full[s], tx);
-          tma_load_2d(dst, &tmW, &full[s], ks * (W4_SLAB_K / 2), n0);
+          tma_load_3d(dst, &tmW, &full[s], ks * (W4_SLAB_K / 2), n0, b);
           if (SCALED) {
             const int srow = (p.group <= W4_SLAB_K) ? ks * p.scale_rows : (ks * W4_SLAB_K) / p.group;
-            tma_load_2d(dst + W4_RAW_PACKED, &tmS, &full[s], n0, srow);
+            tma_load_3d(dst + W4_RAW_PACKED, &tmS, &full[s], n0, srow, b);
           }
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb)
-            tma_load_2d(dst + W4_RAW_BYTES + kb * Cfg::A_KB_BYTES, &tmA, &full[s], ks * W4_SLAB_K + kb * 64, m0);
+            tma_load_3d(dst + W4_RAW_BYTES + kb * Cfg::A_KB_BYTES, &tmA, &full[s], ks * W4_SLAB_K + kb * 64, m0, b);
           issued_mask |= 1u << s;
           parity_mask = (parity_mask & ~(1u << s)) | (phase << s);
           if (++s == ST) { s = 0; phase ^= 1u; }
@@ -176,7 +176,6 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   const int gshift = 31 - __clz(p.group);
   const bool small_group = p.group <= W4_SLAB_K;
   const uint32_t s_off = (uint32_t)(W4_RAW_PACKED + (16 * rb + g) * 2);
-  uint16_t* Cout = reinterpret_cast<uint16_t*>(p.C);
   const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
 
   int s = 0;
@@ -235,8 +234,9 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 
     // ---- segment end: add the two K halves in shared memory, then write the tile or its partial sum
     const bool full_tile = (ks0 == 0 && ks1 == p.KS);
-    const int n0 = (tile / p.m_tiles) * W4_BN;
-    const int m0 = (tile % p.m_tiles) * MT;
+    int b, n0, m0;
+    w4_tile_coords(p, tile, MT, b, n0, m0);
+    uint16_t* Cout = reinterpret_cast<uint16_t*>(p.C) + (size_t)b * p.M * p.N;
     float* r0 = red + (2 * c) * W4_BN + 16 * rb + g;
     if (kh == 1) {
       r0[0] = acc[0];

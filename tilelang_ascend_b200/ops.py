@@ -197,14 +197,15 @@ def simple_quant_matmul(M: int, N: int, K: int, scale_size, block_M: int, block_
 _ws_cache = {}
 
 
-def _w4a16_workspace(lib, M, N, K, device, stream_handle):
-    """Scratch buffer (split-K partial sums + arrival counters), one per (device, stream) and size class.
+def _w4a16_workspace(lib, batch, M, N, K, device, stream_handle):
+    """Scratch buffer (split-K partial sums + arrival counters + prepared activations), one per
+    (device, stream), grown on demand.
 
     The counters must start at zero and the kernel leaves them zero, so the buffer is zeroed once, at
     creation.  Launches on different streams get different buffers because they may overlap on the GPU."""
-    need = lib.qgemm_w4a16_workspace_bytes(M, N, K)
+    need = lib.qgemm_w4a16_batched_workspace_bytes(batch, M, N, K)
     if need < 0:
-        raise _lib.QGemmError("qgemm_w4a16_workspace_bytes: " + _lib.last_error())
+        raise _lib.QGemmError("qgemm_w4a16_batched_workspace_bytes: " + _lib.last_error())
     key = (device.index, stream_handle)
     ws = _ws_cache.get(key)
     if ws is None or ws.numel() < need:
@@ -215,7 +216,11 @@ def _w4a16_workspace(lib, M, N, K, device, stream_handle):
 
 def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None, stream=None, status=None):
     """``C[M,N] = A[M,K] @ W[N,K].T`` with ``W = (unpack_u4(B_packed) - zeros).half() * scales[k // g, n]``
-    (or the raw nibble values when ``scales is None``).  CUDA tensors in, CUDA tensor out."""
+    (or the raw nibble values when ``scales is None``).  CUDA tensors in, CUDA tensor out.
+
+    Batched form: ``A[Batch,M,K]``, ``B_packed[Batch,N,K/2]``, ``scales[Batch,K/g,N]`` -> ``C[Batch,M,N]``,
+    independent problems of one shape in a single launch (the batch dimension of ``simple_quant_batch_matmul``
+    carried over to the W4A16 operator)."""
     lib = _lib.load()
     _require_cuda(A, "A")
     dev = A.device
@@ -224,12 +229,15 @@ def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None
     out_dtype = A.dtype if out_dtype is None else _dt(out_dtype)
     if out_dtype not in (torch.float16, torch.bfloat16):
         raise ValueError("output dtype must be float16 or bfloat16")
-    if A.dim() != 2 or B_packed.dim() != 2:
-        raise ValueError("A must be [M, K] and B_packed [N, K/2]")
-    M, K = A.shape
-    N = B_packed.shape[0]
-    _check_tensor(A, 0, "A", A.dtype, (M, K), dev)
-    _check_tensor(B_packed, 1, "B_packed", torch.uint8, (N, K // 2), dev)
+    if A.dim() not in (2, 3) or B_packed.dim() != A.dim():
+        raise ValueError("A must be [M, K] and B_packed [N, K/2] (or both with a leading batch dimension)")
+    batched = A.dim() == 3
+    batch = A.shape[0] if batched else 1
+    lead = (batch,) if batched else ()
+    M, K = A.shape[-2], A.shape[-1]
+    N = B_packed.shape[-2]
+    _check_tensor(A, 0, "A", A.dtype, lead + (M, K), dev)
+    _check_tensor(B_packed, 1, "B_packed", torch.uint8, lead + (N, K // 2), dev)
     if K % 2 != 0:
         raise ValueError("K must be divisible by 2 (INT4 packed format)")
     if scales is not None:
@@ -239,16 +247,16 @@ def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None
             group_size = K
         if K % group_size != 0:
             raise ValueError("group_size must divide K")
-        _check_tensor(scales, 2, "scales", torch.float16, (K // group_size, N), dev)
+        _check_tensor(scales, 2, "scales", torch.float16, lead + (K // group_size, N), dev)
     else:
         zeros, group_size = 0, K
     sh = _stream_handle(stream, dev)
-    C = torch.empty((M, N), dtype=out_dtype, device=dev)
+    C = torch.empty(lead + (M, N), dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
-        ws, need = _w4a16_workspace(lib, M, N, K, dev, sh)
-        rc = lib.qgemm_w4a16(A.data_ptr(), B_packed.data_ptr(), _ptr(scales), int(zeros), int(group_size),
-                             C.data_ptr(), ws.data_ptr(), need, M, N, K, _ABI_DT[A.dtype], _ABI_DT[out_dtype],
-                             _ptr(status), sh)
+        ws, need = _w4a16_workspace(lib, batch, M, N, K, dev, sh)
+        rc = lib.qgemm_w4a16_batched(A.data_ptr(), B_packed.data_ptr(), _ptr(scales), int(zeros), int(group_size),
+                                     C.data_ptr(), ws.data_ptr(), need, batch, M, N, K, _ABI_DT[A.dtype],
+                                     _ABI_DT[out_dtype], _ptr(status), sh)
     _lib.check(rc, "qgemm_w4a16")
     return C
 
