@@ -6,8 +6,9 @@
 
 Headline workload (N = 1): BASELINE config[1], the W4A16 decode GEMM M=16, K=4096, N=4096, group 128,
 zero point 8, fp16.  One problem is only 8.9 MB, far below the L2 size, so a *step* is one pass over
-LAYERS = 32 distinct weight sets of that shape (285 MB > L2): per layer one small activation pre-pass
-and one GEMM kernel, 64 launches replayed from one CUDA graph.  `value` is algorithmic bytes (each input read once, output written once) over device time, GB/s,
+LAYERS = 32 distinct weight sets of that shape (285 MB > L2), issued as one batched call (one small
+activation pre-pass and one GEMM launch, replayed from a CUDA graph); the same work issued as 32 separate
+calls is timed too and reported under `per_layer_launch`.  `value` is algorithmic bytes (each input read once, output written once) over device time, GB/s,
 whole job over all ranks.  With N > 1 the headline config does not shard ("replicas only"): every rank
 runs its own replica (weak scaling).  The sharded configurations (config 4 by batch, config 5 by weight
 columns with an all-gather of outputs) and the other single-GPU configurations are measured in the same
@@ -38,7 +39,7 @@ CFG2 = dict(M=16, K=4096, N=4096, group=128)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the committed ncu
 # summary under profiles/.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 8847104  # profiles/w4a16_gemm_cfg2_headline.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 290221824  # profiles/w4a16_gemm_cfg2_headline.md (283.5 MB read + 6.7 MB written)
 
 
 def w4a16_bytes(M, K, N, group, out_bytes=2, a_bytes=2):
@@ -192,13 +193,22 @@ def run_ours(args):
     dev_layers = [tuple(t.cuda(non_blocking=True) for t in lay) for lay in host_layers]
     torch.cuda.synchronize()
     outs = [None] * LAYERS
+    # The step's 32 weight sets as one batched problem: [32, M, K], [32, N, K/2], [32, K/g, N].
+    Ab = torch.stack([l[0] for l in dev_layers]).contiguous()
+    Pb = torch.stack([l[1] for l in dev_layers]).contiguous()
+    Sb = torch.stack([l[2] for l in dev_layers]).contiguous()
+    batched_out = [None]
+
+    def launch_batched():
+        batched_out[0] = q.w4a16_gemm(Ab, Pb, Sb, 8, CFG2["group"])
 
     def launch_all():
         for i, (A, P, S) in enumerate(dev_layers):
             outs[i] = q.w4a16_gemm(A, P, S, 8, CFG2["group"])
 
     stream = torch.cuda.Stream()
-    step, launch_mode = make_graph_step(launch_all, stream)
+    step, launch_mode = make_graph_step(launch_batched, stream)
+    step_single, _ = make_graph_step(launch_all, stream)
     bytes_step = LAYERS * w4a16_bytes(**CFG2)
     with torch.cuda.stream(stream):
         with ClockSampler(local) as clk:
@@ -208,10 +218,15 @@ def run_ours(args):
             while time.time() < t_end:
                 step()
             torch.cuda.synchronize()
+        ms_single = timed(step_single, args.steps, args.warmup, world)
     value = world * bytes_step * args.steps / (ms * 1e-3) / 1e9
     ms_per_step = ms / args.steps
-    launch_us = ms_per_step * 1e3 / LAYERS
-    achieved = w4a16_bytes(**CFG2) / (launch_us * 1e-6) / 1e9
+    launch_us = ms_per_step * 1e3  # one batched GEMM launch (plus its activation pre-pass) per step
+    achieved = bytes_step / (launch_us * 1e-6) / 1e9
+    per_layer = {"what": "the same 32 weight sets as 32 separate calls (one pre-pass + one GEMM launch each)",
+                 "ms_per_step": round(ms_single / args.steps, 5),
+                 "value": round(world * bytes_step * args.steps / (ms_single * 1e-3) / 1e9, 2), "unit": "GB/s",
+                 "us_per_call": round(ms_single / args.steps * 1e3 / LAYERS, 3)}
 
     # end to end through the reference-facing wrapper: host tensors in, host tensor out, every step
     wrapper = q.dequant_gemm_fp16_wrapper(CFG2["M"], CFG2["N"], CFG2["K"], 128, 256, 64, "float16", "float16")
@@ -241,17 +256,19 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 (int4 weights, fp32 accumulate)",
             "data": "synthetic",
             "config": {"workload": "BASELINE configs[1]: W4A16 dequantize_gemm decode M=16 K=4096 N=4096 group=128 zero=8 fp16; "
-                                   f"one step = {LAYERS} distinct weight sets ({LAYERS * 8.9:.0f} MB > L2, so no L2 flush needed)",
+                                   f"one step = {LAYERS} distinct weight sets ({LAYERS * 8.9:.0f} MB > L2, so no L2 flush needed), "
+                                   "issued as ONE batched call w4a16_gemm(A[32,M,K], B_packed[32,N,K/2], scales[32,K/g,N])",
                        "layers_per_step": LAYERS, "launch": launch_mode,
                        "multi_gpu": "replicas only for this config; sharded configs are under suite"},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                         "kernel": "w4a16_gemm_kernel<16,f16> (time per layer includes its w4a16_prepare_activations pre-pass)",
+                         "kernel": "w4a16_gemm_kernel<16,f16>, batch 32 (time includes its w4a16_prepare_activations pre-pass)",
                          "us_per_launch": round(launch_us, 3),
-                         "algorithmic_bytes_per_launch": w4a16_bytes(**CFG2), "peak_source": peaks_src + " (copy)"},
+                         "algorithmic_bytes_per_launch": bytes_step, "peak_source": peaks_src + " (copy)"},
+            "per_layer_launch": per_layer,
             "e2e": {"value": round(e2e_value, 3), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "api": "dequant_gemm_fp16_wrapper(CPU tensors) -> CPU tensor"},
-            "gpu_launches": world * LAYERS * KERNELS_PER_LAYER * args.steps,
+            "gpu_launches": world * KERNELS_PER_LAYER * args.steps,
             "clocks": clk.summary(),
         }
         if cpu_base is not None:
@@ -408,8 +425,15 @@ def run_case(args):
         A, P, S = [t.cuda() for t in oc.make_config_inputs(args.case, M=M)]
         sets = 20 if args.case == "cfg2" else 2
         Ps = [P] + [torch.randint(0, 256, P.shape, dtype=torch.uint8, device="cuda") for _ in range(sets - 1)]
-        for i in range(n):
-            C = q.w4a16_gemm(A, Ps[i % sets], S, 8, 128)
+        if args.batch > 1:  # the bench headline: `batch` weight sets of this shape in one launch
+            Pb = torch.randint(0, 256, (args.batch,) + tuple(P.shape), dtype=torch.uint8, device="cuda")
+            Ab = A.unsqueeze(0).repeat(args.batch, 1, 1).contiguous()
+            Sb = S.unsqueeze(0).repeat(args.batch, 1, 1).contiguous()
+            for i in range(n):
+                C = q.w4a16_gemm(Ab, Pb, Sb, 8, 128)
+        else:
+            for i in range(n):
+                C = q.w4a16_gemm(A, Ps[i % sets], S, 8, 128)
     torch.cuda.synchronize()
     print(json.dumps({"case": args.case, "launches": n, "checksum": float(C.float().abs().mean())}))
 
@@ -426,6 +450,7 @@ def main():
                     help="profiling helper: launch one configuration a few times and exit")
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=1)
     args = ap.parse_args()
     if args.case is not None:
         return run_case(args)
