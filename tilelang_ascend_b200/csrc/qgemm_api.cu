@@ -61,9 +61,10 @@ int set_smem_w8() {
 }
 template <int FLUSH>
 int set_smem_w4d() {
-  using C = qg::W4DCfg;
-  if (set_smem(qg::w4a16_decode_kernel<FLUSH, false>, C::SMEM_BYTES)) return -1;
-  if (set_smem(qg::w4a16_decode_kernel<FLUSH, true>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_decode_kernel<FLUSH, 1, false>, qg::W4DCfg<1>::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_decode_kernel<FLUSH, 1, true>, qg::W4DCfg<1>::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_decode_kernel<FLUSH, 2, false>, qg::W4DCfg<2>::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_decode_kernel<FLUSH, 2, true>, qg::W4DCfg<2>::SMEM_BYTES)) return -1;
   return 0;
 }
 int set_smem_w8_pair() {
@@ -154,31 +155,36 @@ int launch_w4(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUt
   return 0;
 }
 
-template <int FLUSH>
-int launch_w4d(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
-               const qg::W4A16Params& p, int grid, cudaStream_t s) {
+template <int FLUSH, int NB>
+int launch_w4d_nb(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
+                  const qg::W4A16Params& p, int grid, cudaStream_t s) {
   if (bf)
-    qg::w4a16_decode_kernel<FLUSH, true><<<grid, qg::W4D_THREADS, qg::W4DCfg::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
+    qg::w4a16_decode_kernel<FLUSH, NB, true><<<grid, qg::W4D_THREADS, qg::W4DCfg<NB>::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
   else
-    qg::w4a16_decode_kernel<FLUSH, false><<<grid, qg::W4D_THREADS, qg::W4DCfg::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
+    qg::w4a16_decode_kernel<FLUSH, NB, false><<<grid, qg::W4D_THREADS, qg::W4DCfg<NB>::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
   CUDA_OK(cudaGetLastError());
   return 0;
 }
-
+template <int FLUSH>
+int launch_w4d(bool bf, int mt, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
+               const qg::W4A16Params& p, int grid, cudaStream_t s) {
+  if (mt == 16) return launch_w4d_nb<FLUSH, 2>(bf, tmW, tmS, tmA, p, grid, s);
+  return launch_w4d_nb<FLUSH, 1>(bf, tmW, tmS, tmA, p, grid, s);
+}
 // Token counts up to this use the register-operand streaming kernel (w4a16_decode.cuh); above it the
 // tcgen05 kernel (w4a16.cuh).
 int w4_decode_max_m() {
   static int v = -1;
   if (v < 0) {
     v = 8;
-    if (const char* e = getenv("QGEMM_W4_DECODE_MAX_M")) v = atoi(e) < 8 ? atoi(e) : 8;
+    if (const char* e = getenv("QGEMM_W4_DECODE_MAX_M")) v = atoi(e) < 16 ? atoi(e) : 16;
   }
   return v;
 }
 bool w4_use_decode(int64_t M) { return M <= w4_decode_max_m(); }
 // Token-tile height: 8 for the decode kernel, 16..128 for the tcgen05 kernel.
 int w4_pick_mt(int64_t M) {
-  if (w4_use_decode(M)) return 8;
+  if (w4_use_decode(M)) return M <= 8 ? 8 : 16;
   return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
 }
 
@@ -449,10 +455,10 @@ int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scal
     CUDA_OK(cudaGetLastError());
   }
   if (w4_use_decode(M)) {
-    if (scales == nullptr) return launch_w4d<0>(bf, tmW, tmS, tmA, p, (int)grid, s);
-    if (group >= 128) return launch_w4d<4>(bf, tmW, tmS, tmA, p, (int)grid, s);
-    if (group == 64) return launch_w4d<2>(bf, tmW, tmS, tmA, p, (int)grid, s);
-    return launch_w4d<1>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    if (scales == nullptr) return launch_w4d<0>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);
+    if (group >= 128) return launch_w4d<4>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);
+    if (group == 64) return launch_w4d<2>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);
+    return launch_w4d<1>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);
   }
   switch (mt) {
     case 16: return launch_w4<16>(bf, tmW, tmS, tmA, p, (int)grid, s);

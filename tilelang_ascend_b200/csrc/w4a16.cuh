@@ -16,8 +16,8 @@
 // contributor of that tile (found with a counter, never by waiting) adds the partials in a fixed order,
 // so results do not depend on arrival order.
 //   warp 0       TMA: packed weights [128 rows x 128 B] + the slab's scales into the "raw" ring
-//   warp 1       tcgen05.mma kind::f16 issuer (A from TMEM, B from shared memory), fp32 accumulators in
-//                tensor memory, double buffered
+//   warp 1, 23..25  tcgen05.mma kind::f16 issuers (A from TMEM, B from shared memory), one fp32 accumulator
+//                each in tensor memory, double buffered
 //   warp 2       TMA: activation tiles [MT x 256 k] into their own ring
 //   warps 3..6   epilogue (TMEM -> registers -> global / scratch, split-K reduction)
 //   warps 7..22  dequant: lop3 magic-number conversion, (q - zero) * s in f16x2, tcgen05.st
@@ -51,7 +51,9 @@ constexpr int W4_BN = 128;        // weight rows per tile
 constexpr int W4_SLAB_K = 256;    // K per pipeline item: 128 packed bytes per row
 constexpr int W4_DQ_WARPS = 16;
 constexpr int W4_FIRST_DQ_WARP = 7;
-constexpr int W4_THREADS = (W4_FIRST_DQ_WARP + W4_DQ_WARPS) * 32;  // 736
+constexpr int W4_MAX_MMA_WARPS = 4;
+constexpr int W4_FIRST_XMMA_WARP = W4_FIRST_DQ_WARP + W4_DQ_WARPS;          // extra MMA-issuing warps 23..25
+constexpr int W4_THREADS = (W4_FIRST_XMMA_WARP + W4_MAX_MMA_WARPS - 1) * 32;  // 832
 constexpr int W4_RAW_PACKED = W4_BN * 128;         // 16 KB
 constexpr int W4_RAW_BYTES = W4_RAW_PACKED + 2048; // + up to 8 scale rows of 128 halves
 constexpr int W4_W_COLS = W4_SLAB_K / 2;           // TMEM columns per slab of dequantised weights
@@ -62,10 +64,14 @@ struct W4Cfg {
   // so that ring must cover the load latency plus the dequant and MMA time of the items in between.
   static constexpr int RAW_STAGES = (MT == 16) ? 8 : (MT == 32 ? 7 : (MT == 64 ? 5 : 4));
   static constexpr int A_STAGES = (MT == 16) ? 9 : (MT == 32 ? 6 : (MT == 64 ? 4 : 2));
-  static constexpr int W_STAGES = (MT <= 64) ? 3 : 2;
+  // One warp can issue a tcgen05.mma only every ~49 cycles (measured), far longer than a 16-token MMA runs,
+  // so MMAW warps issue the K steps of a slab in parallel, each into its own accumulator; the epilogue adds
+  // the MMAW accumulators in a fixed order.
+  static constexpr int MMAW = (MT <= 32) ? 4 : (MT == 64 ? 2 : 1);
+  static constexpr int W_STAGES = (MT == 16) ? 3 : 2;
   static constexpr int A_KB_BYTES = MT * 128;          // one 64-wide K block of activations
   static constexpr int A_BYTES = 4 * A_KB_BYTES;       // one 256-wide slab
-  static constexpr int ACC_COLS = 2 * MT;              // two accumulator buffers
+  static constexpr int ACC_COLS = 2 * MMAW * MT;       // two buffers of MMAW accumulators
   static constexpr int TMEM_COLS = 512;
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_BYTES = RAW_STAGES * W4_RAW_BYTES + A_STAGES * A_BYTES + BAR_BYTES + 1024;
@@ -197,14 +203,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     for (int s = 0; s < AS; ++s) {
       mbar_init(&a_full[s], 1);
-      mbar_init(&a_empty[s], 1);
+      mbar_init(&a_empty[s], Cfg::MMAW);
     }
     for (int s = 0; s < WS; ++s) {
       mbar_init(&w_full[s], W4_DQ_WARPS);
-      mbar_init(&w_empty[s], 1);
+      mbar_init(&w_empty[s], Cfg::MMAW);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&tfull[i], 1);
+      mbar_init(&tfull[i], Cfg::MMAW);
       mbar_init(&tempty[i], 4);
     }
     mbar_init(drain, 1);
@@ -303,14 +309,14 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
       }
     }
-  } else if (warp == 1) {
-    // -------------------------------------------------------------- MMA issuer
-    // The whole warp walks the loop with identical (warp-uniform) operands; lane 0 issues.
-    {
+  } else if (warp == 1 || warp >= W4_FIRST_XMMA_WARP) {
+    // -------------------------------------------------------------- MMA issuers
+    // Issuer w of MMAW takes the K steps kk = w, w + MMAW, ... of every slab and accumulates them into its
+    // own accumulator (columns w*MT of the buffer).
+    const int mw = (warp == 1) ? 0 : (warp - W4_FIRST_XMMA_WARP + 1);
+    if (mw < Cfg::MMAW && lane == 0) {
       constexpr uint32_t idesc = make_idesc(ACC_F32, FMT_F16, FMT_F16, 0, 0, W4_BN, MT);
-      const uint32_t leader = (lane == 0) ? 1u : 0u;
-      // K-major activation descriptor without its start-address field (filled in per stage).
-      const uint64_t desc_hi = make_desc_kmajor(0);
+      const uint64_t desc_hi = make_desc_kmajor(0);  // K-major activation descriptor without its start address
       const uint32_t a_base_u32 = smem_u32(a_base);
       int ws = 0, as = 0;
       uint32_t wphase = 0, aphase = 0;
@@ -319,31 +325,32 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       while (ok && seg.next(tile, ks0, ks1)) {
         const int buf = it & 1;
         const uint32_t tphase = (it >> 1) & 1;
-        if (!mbar_wait_warp(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+        if (!mbar_wait(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t d = tmem_base + buf * MT;
-        uint32_t started = 0;  // 0 for the first MMA of the segment: overwrite the accumulator
+        const uint32_t d = tmem_base + buf * (Cfg::MMAW * MT) + mw * MT;
+        uint32_t started = 0;  // 0 for this issuer's first MMA of the segment: overwrite the accumulator
         for (int ks = ks0; ks < ks1; ++ks) {
-          if (!mbar_wait_warp(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
-          if (!mbar_wait_warp(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+          if (!mbar_wait(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+          if (!mbar_wait(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
           tc_fence_after_sync();
           const uint64_t adesc0 = desc_hi | (uint64_t)(((a_base_u32 + as * Cfg::A_BYTES) & 0x3FFFFu) >> 4);
           const uint32_t tW = tmem_w + ws * W4_W_COLS;
 #pragma unroll
-          for (int kk = 0; kk < W4_SLAB_K / 16; ++kk) {  // 16 k per MMA: 8 TMEM columns, 32 bytes of smem
+          for (int j = 0; j < (W4_SLAB_K / 16) / Cfg::MMAW; ++j) {  // 16 k per MMA: 8 TMEM columns, 32 bytes of smem
+            const int kk = j * Cfg::MMAW + mw;
             const uint32_t off = (uint32_t)(((kk >> 2) * Cfg::A_KB_BYTES + (kk & 3) * 32) >> 4);
-            umma_f16_ts_elect(leader, d, tW + kk * 8, adesc0 + off, idesc, started);
+            umma_f16_ts(d, tW + kk * 8, adesc0 + off, idesc, started);
             started = 1u;
           }
-          umma_commit_elect(leader, &w_empty[ws]);
-          umma_commit_elect(leader, &a_empty[as]);
+          umma_commit(&w_empty[ws]);
+          umma_commit(&a_empty[as]);
           if (++ws == WS) { ws = 0; wphase ^= 1u; }
           if (++as == AS) { as = 0; aphase ^= 1u; }
         }
-        if (ok) umma_commit_elect(leader, &tfull[buf]);
+        if (ok) umma_commit(&tfull[buf]);
         ++it;
       }
-      if (!ok && lane == 0) {
+      if (!ok && mw == 0) {
         umma_commit(drain);
         const uint64_t t0 = global_timer_ns();
         while (!mbar_try_wait(drain, 0)) {
@@ -370,13 +377,22 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const bool ok = mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE);
       if (ok) {
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * MT;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (Cfg::MMAW * MT);
 #pragma unroll 1
         for (int c = 0; c < MT / CH; ++c) {
           uint32_t r[CH];
           if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + c * CH, r);
           else tmem_ld_32x32b_x32(taddr + c * CH, r);
           tmem_ld_wait();
+#pragma unroll
+          for (int a = 1; a < Cfg::MMAW; ++a) {  // add the other issuers' accumulators, fixed order
+            uint32_t r2[CH];
+            if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + a * MT + c * CH, r2);
+            else tmem_ld_32x32b_x32(taddr + a * MT + c * CH, r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+          }
           if (full_tile) {
             if (n < p.N) {
 #pragma unroll
@@ -458,7 +474,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         }
       }
     }
-  } else if (warp >= W4_FIRST_DQ_WARP) {
+  } else if (warp >= W4_FIRST_DQ_WARP && warp < W4_FIRST_XMMA_WARP) {
     // ----------------------------------------------------------------- dequant
     // Warp (q, j): TMEM lanes 32q..32q+31 (the quadrant this warp may touch), K sub-range [64j, 64j+64) of
     // the slab = packed 16-byte chunks 2j and 2j+1 of the row = 32 TMEM columns.

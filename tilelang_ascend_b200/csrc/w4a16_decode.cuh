@@ -1,6 +1,6 @@
 // W4A16 decode variant (few tokens, memory bound) for sm_100a.
 //
-// With at most 8 tokens the GEMM is a weight stream: every packed byte is read once from HBM and used for a
+// With at most 16 tokens the GEMM is a weight stream: every packed byte is read once from HBM and used for a
 // handful of tokens.  Measured on B200, tcgen05.mma with a 16-token N costs about 94 cycles per K=16 step
 // whatever the accumulator layout (fixed tensor-memory operand/accumulator traffic per instruction), i.e.
 // 0.8 us per 16 KB of packed weights against 0.37 us of HBM time, so this variant keeps the weights in
@@ -28,11 +28,12 @@ constexpr int W4D_CWARPS = 16;
 constexpr int W4D_THREADS = (1 + W4D_CWARPS) * 32;  // 544
 constexpr int W4D_CTHREADS = W4D_CWARPS * 32;       // 512
 
+template <int NB>  // NB blocks of 8 tokens (one mma.sync N each)
 struct W4DCfg {
-  static constexpr int MT = 8;                                // tokens per tile (one mma.sync N)
+  static constexpr int MT = 8 * NB;                           // tokens per tile
   static constexpr int A_KB_BYTES = MT * 128;                 // one 64-wide K block of activations
   static constexpr int STAGE_BYTES = W4_RAW_BYTES + 4 * A_KB_BYTES;
-  static constexpr int STAGES = 9;
+  static constexpr int STAGES = (NB == 1) ? 9 : 7;
   static constexpr int RED_BYTES = MT * W4_BN * 4;            // fp32 tile for the K-half exchange / epilogue
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RED_BYTES + BAR_BYTES + 1024;
@@ -67,11 +68,11 @@ __device__ __forceinline__ void w4d_cbar() { asm volatile("bar.sync 1, 512;" :::
 
 // FLUSH: number of 32-wide K chunks per quantisation group inside a warp's 128-wide K half (4 when the
 // group is 128 or larger, 2 for 64, 1 for 32); 0 = no scales (raw nibble values).
-template <int FLUSH, bool OUT_BF16>
+template <int FLUSH, int NB, bool OUT_BF16>
 __global__ void __launch_bounds__(W4D_THREADS, 1)
 w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
                     const __grid_constant__ CUtensorMap tmA, const W4A16Params p) {
-  using Cfg = W4DCfg;
+  using Cfg = W4DCfg<NB>;
   constexpr int MT = Cfg::MT;
   constexpr int ST = Cfg::STAGES;
   constexpr bool SCALED = FLUSH != 0;
@@ -182,43 +183,52 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   uint32_t phase = 0;
   bool ok = true;
   while (seg.next(tile, ks0, ks1)) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    float acc2[4] = {0.f, 0.f, 0.f, 0.f};  // second chain when unscaled
+    float acc[NB][4], acc2[NB][4];  // acc2: second chain when unscaled
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { acc[nb][i] = 0.f; acc2[nb][i] = 0.f; }
 
     for (int ks = ks0; ks < ks1; ++ks) {
       if (ok) ok = mbar_wait_warp(&full[s], phase, ctl, ST_TIMEOUT_DEQUANT);
       if (ok) {
         const uint8_t* stg = smem + s * Cfg::STAGE_BYTES;
-        float pa[4], pb[4];  // two independent accumulation chains per group
+        float pa[NB][4], pb[NB][4];  // two independent accumulation chains per group
 #pragma unroll
         for (int kc = 0; kc < 4; ++kc) {
           const uint32_t x_lo = *reinterpret_cast<const uint32_t*>(stg + w_off[kc]);
           const uint32_t x_hi = *reinterpret_cast<const uint32_t*>(stg + w_off[kc] + 8 * 128);
-          const uint4 av = *reinterpret_cast<const uint4*>(stg + a_off[kc]);
           uint32_t hl[4], hh[4];
           w4d_convert8(x_lo, sub_lo, sub_hi, hl);
           w4d_convert8(x_hi, sub_lo, sub_hi, hh);
-          if constexpr (!SCALED) {
-            w4d_mma(acc, hl[0], hh[0], hl[1], hh[1], av.x, av.y, acc);
-            w4d_mma(acc2, hl[2], hh[2], hl[3], hh[3], av.z, av.w, acc2);
-          } else {
-            if (kc % FLUSH == 0) {
-              w4d_mma(pa, hl[0], hh[0], hl[1], hh[1], av.x, av.y, zero4);
-              w4d_mma(pb, hl[2], hh[2], hl[3], hh[3], av.z, av.w, zero4);
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            const uint4 av = *reinterpret_cast<const uint4*>(stg + a_off[kc] + nb * 8 * 128);
+            if constexpr (!SCALED) {
+              w4d_mma(acc[nb], hl[0], hh[0], hl[1], hh[1], av.x, av.y, acc[nb]);
+              w4d_mma(acc2[nb], hl[2], hh[2], hl[3], hh[3], av.z, av.w, acc2[nb]);
+            } else if (kc % FLUSH == 0) {
+              w4d_mma(pa[nb], hl[0], hh[0], hl[1], hh[1], av.x, av.y, zero4);
+              w4d_mma(pb[nb], hl[2], hh[2], hl[3], hh[3], av.z, av.w, zero4);
             } else {
-              w4d_mma(pa, hl[0], hh[0], hl[1], hh[1], av.x, av.y, pa);
-              w4d_mma(pb, hl[2], hh[2], hl[3], hh[3], av.z, av.w, pb);
+              w4d_mma(pa[nb], hl[0], hh[0], hl[1], hh[1], av.x, av.y, pa[nb]);
+              w4d_mma(pb[nb], hl[2], hh[2], hl[3], hh[3], av.z, av.w, pb[nb]);
             }
+          }
+          if constexpr (SCALED) {
             if ((kc + 1) % FLUSH == 0) {
               // end of a quantisation group (or of this warp's 128 k of a larger group): scale the partial sums
               const int srow = small_group ? ((kh * 128 + kc * 32) >> gshift) : 0;
               const __half* sp = reinterpret_cast<const __half*>(stg + s_off) + srow * W4_BN;
               const float s_lo = __half2float(sp[0]);
               const float s_hi = __half2float(sp[8]);
-              acc[0] = fmaf(pa[0] + pb[0], s_lo, acc[0]);
-              acc[1] = fmaf(pa[1] + pb[1], s_lo, acc[1]);
-              acc[2] = fmaf(pa[2] + pb[2], s_hi, acc[2]);
-              acc[3] = fmaf(pa[3] + pb[3], s_hi, acc[3]);
+#pragma unroll
+              for (int nb = 0; nb < NB; ++nb) {
+                acc[nb][0] = fmaf(pa[nb][0] + pb[nb][0], s_lo, acc[nb][0]);
+                acc[nb][1] = fmaf(pa[nb][1] + pb[nb][1], s_lo, acc[nb][1]);
+                acc[nb][2] = fmaf(pa[nb][2] + pb[nb][2], s_hi, acc[nb][2]);
+                acc[nb][3] = fmaf(pa[nb][3] + pb[nb][3], s_hi, acc[nb][3]);
+              }
             }
           }
         }
@@ -229,7 +239,9 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     }
     if constexpr (!SCALED) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[i] += acc2[i];
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[nb][i] += acc2[nb][i];
     }
 
     // ---- segment end: add the two K halves in shared memory, then write the tile or its partial sum
@@ -239,17 +251,25 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     uint16_t* Cout = reinterpret_cast<uint16_t*>(p.C) + (size_t)b * p.M * p.N;
     float* r0 = red + (2 * c) * W4_BN + 16 * rb + g;
     if (kh == 1) {
-      r0[0] = acc[0];
-      r0[W4_BN] = acc[1];
-      r0[8] = acc[2];
-      r0[W4_BN + 8] = acc[3];
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        float* r = r0 + nb * 8 * W4_BN;
+        r[0] = acc[nb][0];
+        r[W4_BN] = acc[nb][1];
+        r[8] = acc[nb][2];
+        r[W4_BN + 8] = acc[nb][3];
+      }
     }
     w4d_cbar();
     if (kh == 0) {
-      r0[0] += acc[0];
-      r0[W4_BN] += acc[1];
-      r0[8] += acc[2];
-      r0[W4_BN + 8] += acc[3];
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        float* r = r0 + nb * 8 * W4_BN;
+        r[0] += acc[nb][0];
+        r[W4_BN] += acc[nb][1];
+        r[8] += acc[nb][2];
+        r[W4_BN + 8] += acc[nb][3];
+      }
     }
     w4d_cbar();
     if (*abort_flag) break;  // uniform: read after the barrier
