@@ -10,6 +10,9 @@
 //   warp 0        TMA producer: per 256-wide K slab one stage = packed weights [128 rows x 128 B],
 //                 the slab's scales, and the prepared activations [MT tokens x 256 k]
 //   warps 1..16   compute: warp (rb, kh) owns weight rows 16*rb .. 16*rb+15 and the K half kh of every slab
+//   warp 17       finisher: adds the two K halves of a finished segment, writes the tile or runs the split-K
+//                 hand-over (partial sum, fence, arrival counter, fixed-order reduction by the last arriver),
+//                 so that the compute warps go straight on to the next segment
 //
 // Numerics: products (q - zero) * a are exact in the tensor core and accumulate in fp32 per quantisation
 // group; the group's fp32 sum is then multiplied by the group scale.  With one token set to a unit vector
@@ -25,8 +28,8 @@
 namespace qg {
 
 constexpr int W4D_CWARPS = 16;
-constexpr int W4D_THREADS = (1 + W4D_CWARPS) * 32;  // 544
-constexpr int W4D_CTHREADS = W4D_CWARPS * 32;       // 512
+constexpr int W4D_FIN_WARP = 1 + W4D_CWARPS;        // 17
+constexpr int W4D_THREADS = (2 + W4D_CWARPS) * 32;  // 576
 
 template <int NB>  // NB blocks of 8 tokens (one mma.sync N each)
 struct W4DCfg {
@@ -34,7 +37,8 @@ struct W4DCfg {
   static constexpr int A_KB_BYTES = MT * 128;                 // one 64-wide K block of activations
   static constexpr int STAGE_BYTES = W4_RAW_BYTES + 4 * A_KB_BYTES;
   static constexpr int STAGES = (NB == 1) ? 9 : 7;
-  static constexpr int RED_BYTES = MT * W4_BN * 4;            // fp32 tile for the K-half exchange / epilogue
+  static constexpr int RED_TILE = MT * W4_BN;                 // floats of one K half's tile
+  static constexpr int RED_BYTES = 2 * 2 * RED_TILE * 4;      // two buffers x two K halves, handed to the finisher
   static constexpr int BAR_BYTES = 256;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RED_BYTES + BAR_BYTES + 1024;
 };
@@ -64,7 +68,19 @@ __device__ __forceinline__ void w4d_mma(float (&d)[4], uint32_t a0, uint32_t a1,
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 
-__device__ __forceinline__ void w4d_cbar() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+// Four fp32 results -> four f16 / bf16 outputs, one 8-byte store.
+template <bool OUT_BF16>
+__device__ __forceinline__ void w4d_store4(uint16_t* dst, const float4& v) {
+  uint2 o;
+  if (OUT_BF16) {
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+  } else {
+    o.x = pack_f16x2(v.x, v.y);
+    o.y = pack_f16x2(v.z, v.w);
+  }
+  *reinterpret_cast<uint2*>(dst) = o;
+}
 
 // FLUSH: number of 32-wide K chunks per quantisation group inside a warp's 128-wide K half (4 when the
 // group is 128 or larger, 2 for 64, 1 for 32); 0 = no scales (raw nibble values).
@@ -83,8 +99,9 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ST * Cfg::STAGE_BYTES + Cfg::RED_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + ST;
-  volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(empty + ST);
-  volatile uint32_t* epi_flag = abort_flag + 1;
+  uint64_t* red_full = empty + ST;   // [2] compute warps -> finisher
+  uint64_t* red_empty = red_full + 2;  // [2] finisher -> compute warps
+  volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(red_empty + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -94,8 +111,11 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], W4D_CWARPS);
     }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&red_full[i], W4D_CWARPS);
+      mbar_init(&red_empty[i], 1);
+    }
     *abort_flag = 0;
-    *epi_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmA);
@@ -153,13 +173,88 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     return;  // the producer warp takes no part in the compute warps' named barrier
   }
 
+  if (warp == W4D_FIN_WARP) {
+    // ---------------------------------------------------------------- finisher
+    // Lane l owns the float4 column group l of every token row of the tile.
+    int it = 0;
+    while (seg.next(tile, ks0, ks1)) {
+      const int buf = it & 1;
+      const uint32_t rphase = (it >> 1) & 1;
+      ++it;
+      if (!mbar_wait_warp(&red_full[buf], rphase, ctl, ST_TIMEOUT_EPILOGUE)) break;
+      int b, n0, m0;
+      w4_tile_coords(p, tile, MT, b, n0, m0);
+      const int rows = min(MT, p.M - m0);
+      const float4* h0 = reinterpret_cast<const float4*>(red + (size_t)buf * 2 * Cfg::RED_TILE);
+      const float4* h1 = h0 + Cfg::RED_TILE / 4;
+      uint16_t* Cout = reinterpret_cast<uint16_t*>(p.C) + (size_t)b * p.M * p.N;
+      const int n = n0 + 4 * lane;  // N is a multiple of 8 and n of 4: the four columns are inside N together
+      const bool full_tile = (ks0 == 0 && ks1 == p.KS);
+      const int my_slot = (ks1 < p.KS) ? 2 * cta + 1 : 2 * cta;
+      float4* my_part = reinterpret_cast<float4*>(p.ws_partials + (size_t)my_slot * (MT * W4_BN));
+      // Add the two K halves; a whole tile goes straight to C, a split tile's sum to this CTA's partial slot.
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        if (i < rows) {
+          const float4 x = h0[i * 32 + lane], y = h1[i * 32 + lane];
+          const float4 v = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+          if (!full_tile) my_part[i * 32 + lane] = v;
+          else if (n < p.N) w4d_store4<OUT_BF16>(Cout + (size_t)(m0 + i) * p.N + n, v);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&red_empty[buf]);  // the buffer may be refilled
+      if (full_tile) continue;
+
+      // Split tile: count arrivals; the last contributor adds all partials in a fixed order.
+      const long long first_item = (long long)tile * p.KS;
+      const int b_first = w4_owner(T, G, first_item);
+      const int b_last = w4_owner(T, G, first_item + p.KS - 1);
+      __threadfence();
+      __syncwarp();
+      uint32_t last = 0;
+      if (lane == 0) {
+        const uint32_t old = atomicAdd(p.ws_counters + b_first, 1u);
+        if (old == (uint32_t)(b_last - b_first)) {
+          last = 1;
+          p.ws_counters[b_first] = 0;  // every contributor has arrived: leave the counter clean
+        }
+      }
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (!last) continue;
+      __threadfence();
+      for (int i0 = 0; i0 < rows; i0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int cc = b_first; cc <= b_last; ++cc) {  // fixed order: results do not depend on arrival order
+          const long long c_end = w4_range_begin(T, G, cc + 1);
+          const int slot = (c_end >= first_item + p.KS) ? 2 * cc : 2 * cc + 1;
+          const float4* part = reinterpret_cast<const float4*>(p.ws_partials + (size_t)slot * (MT * W4_BN));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (i0 + i < rows) {
+              const float4 x = __ldcg(part + (i0 + i) * 32 + lane);
+              v[i].x += x.x; v[i].y += x.y; v[i].z += x.z; v[i].w += x.w;
+            }
+          }
+        }
+        if (n < p.N) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (i0 + i < rows) w4d_store4<OUT_BF16>(Cout + (size_t)(m0 + i0 + i) * p.N + n, v[i]);
+        }
+      }
+    }
+    return;
+  }
+
   // ------------------------------------------------------------------ compute warps
   const int cw = warp - 1;
   const int rb = cw & 7;    // 16-row block of the tile
   const int kh = cw >> 3;   // K half of every slab
   const int g = lane >> 2;  // mma "group id": weight row g / g+8, token g
   const int c = lane & 3;   // mma "thread in group": K pairs and token pairs
-  const int ctid = cw * 32 + lane;
   const uint32_t zero = (uint32_t)p.zero;
   const uint32_t sub_lo = (0x6400u + zero) * 0x00010001u;
   const uint32_t sub_hi = ((0x5400u + (zero << 4)) | 0x8000u) * 0x00010001u;
@@ -179,7 +274,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   const uint32_t s_off = (uint32_t)(W4_RAW_PACKED + (16 * rb + g) * 2);
   const float zero4[4] = {0.f, 0.f, 0.f, 0.f};
 
-  int s = 0;
+  int s = 0, it = 0;
   uint32_t phase = 0;
   bool ok = true;
   while (seg.next(tile, ks0, ks1)) {
@@ -244,84 +339,23 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         for (int i = 0; i < 4; ++i) acc[nb][i] += acc2[nb][i];
     }
 
-    // ---- segment end: add the two K halves in shared memory, then write the tile or its partial sum
-    const bool full_tile = (ks0 == 0 && ks1 == p.KS);
-    int b, n0, m0;
-    w4_tile_coords(p, tile, MT, b, n0, m0);
-    uint16_t* Cout = reinterpret_cast<uint16_t*>(p.C) + (size_t)b * p.M * p.N;
-    float* r0 = red + (2 * c) * W4_BN + 16 * rb + g;
-    if (kh == 1) {
+    // ---- segment end: hand this warp's K-half sums to the finisher and go on
+    const int buf = it & 1;
+    const uint32_t ephase = ((it >> 1) & 1) ^ 1u;
+    ++it;
+    if (ok) ok = mbar_wait_warp(&red_empty[buf], ephase, ctl, ST_TIMEOUT_DEQUANT);
+    if (!ok) break;  // an expired wait has set the abort flag: every other wait in the CTA gives up too
+    float* r0 = red + (size_t)(buf * 2 + kh) * Cfg::RED_TILE + (2 * c) * W4_BN + 16 * rb + g;
 #pragma unroll
-      for (int nb = 0; nb < NB; ++nb) {
-        float* r = r0 + nb * 8 * W4_BN;
-        r[0] = acc[nb][0];
-        r[W4_BN] = acc[nb][1];
-        r[8] = acc[nb][2];
-        r[W4_BN + 8] = acc[nb][3];
-      }
+    for (int nb = 0; nb < NB; ++nb) {
+      float* r = r0 + nb * 8 * W4_BN;
+      r[0] = acc[nb][0];
+      r[W4_BN] = acc[nb][1];
+      r[8] = acc[nb][2];
+      r[W4_BN + 8] = acc[nb][3];
     }
-    w4d_cbar();
-    if (kh == 0) {
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb) {
-        float* r = r0 + nb * 8 * W4_BN;
-        r[0] += acc[nb][0];
-        r[W4_BN] += acc[nb][1];
-        r[8] += acc[nb][2];
-        r[W4_BN + 8] += acc[nb][3];
-      }
-    }
-    w4d_cbar();
-    if (*abort_flag) break;  // uniform: read after the barrier
-    const int rows = min(MT, p.M - m0);
-    if (full_tile) {
-      for (int idx = ctid; idx < rows * W4_BN; idx += W4D_CTHREADS) {
-        const int m = idx >> 7, nl = idx & 127;
-        if (n0 + nl < p.N) {
-          const float v = red[idx];
-          Cout[(size_t)(m0 + m) * p.N + n0 + nl] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
-                                                            : __half_as_ushort(__float2half_rn(v));
-        }
-      }
-      w4d_cbar();  // `red` is reused by the next segment
-      continue;
-    }
-    // Split tile: publish the partial, count arrivals; the last contributor reduces in a fixed order.
-    const int my_slot = (ks1 < p.KS) ? 2 * cta + 1 : 2 * cta;
-    float* my_part = p.ws_partials + (size_t)my_slot * (MT * W4_BN);
-    for (int idx = ctid; idx < rows * W4_BN; idx += W4D_CTHREADS) my_part[idx] = red[idx];
-    const long long first_item = (long long)tile * p.KS;
-    const int b_first = w4_owner(T, G, first_item);
-    const int b_last = w4_owner(T, G, first_item + p.KS - 1);
-    __threadfence();
-    w4d_cbar();
-    if (ctid == 0) {
-      uint32_t last = 0;
-      const uint32_t old = atomicAdd(p.ws_counters + b_first, 1u);
-      if (old == (uint32_t)(b_last - b_first)) {
-        last = 1;
-        p.ws_counters[b_first] = 0;  // every contributor has arrived: leave the counter clean
-      }
-      *epi_flag = last;
-    }
-    w4d_cbar();
-    const bool is_last = *epi_flag != 0;
-    w4d_cbar();  // epi_flag and `red` may be rewritten only after everyone has read them
-    if (is_last) {
-      __threadfence();
-      for (int idx = ctid; idx < rows * W4_BN; idx += W4D_CTHREADS) {
-        const int m = idx >> 7, nl = idx & 127;
-        float sum = 0.f;
-        for (int cc = b_first; cc <= b_last; ++cc) {  // fixed order: results do not depend on arrival order
-          const long long c_end = w4_range_begin(T, G, cc + 1);
-          const int slot = (c_end >= first_item + p.KS) ? 2 * cc : 2 * cc + 1;
-          sum += __ldcg(p.ws_partials + (size_t)slot * (MT * W4_BN) + idx);
-        }
-        if (n0 + nl < p.N)
-          Cout[(size_t)(m0 + m) * p.N + n0 + nl] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum))
-                                                            : __half_as_ushort(__float2half_rn(sum));
-      }
-    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&red_full[buf]);
   }
 }
 
