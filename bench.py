@@ -317,6 +317,16 @@ def run_suite(q, world, rank, peaks):
                     "frac_of_2x_measured_bf16": round(ops / ms / 1e9 / int8_peak, 4)})
         del A, B
 
+    if world == 1:
+        # the step in front of the W8A8 GEMM: per-token activation quantiser, rows x 8192 bf16 (805 MB moved > L2)
+        Mq, Nq = 32768, 8192
+        X = torch.randn((Mq, Nq), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda()
+        ms = _time_rotating(lambda i: q.act_quant(X), 1, 10, world)
+        by = 3 * Mq * Nq + 4 * Mq
+        res.append({"config": f"act_quant {Mq}x{Nq} bf16 -> int8 + fp32 row scales", "ms": round(ms, 5),
+                    "gbs": round(by / ms / 1e6, 1), "frac_of_measured_hbm": round(by / ms / 1e6 / peaks["hbm_gbs"], 4)})
+        del X
+
     # config 4: batch sharded, no collective
     A, B, sa, sb = oc.make_config_inputs("cfg4")
     A, B, sa, sb = [t.cuda() for t in shard_batches([A, B, sa, sb], world, rank)]
@@ -408,14 +418,18 @@ def run_reference(args):
 
 
 def run_case(args):
-    """A few eager launches of one configuration, for profilers: `--case cfg2|cfg3|cfg4|cfg5 [--m M] [--launches L]`.
+    """A few eager launches of one configuration, for profilers: `--case cfg2|cfg3|cfg4|cfg5|act_quant [--m M] [--launches L]`.
 
     Weight sets rotate so that reads stay L2-cold (cfg2: 20 sets = 160 MB; cfg5: 2 sets = 235 MB)."""
     import tilelang_ascend_b200 as q
     from oracle import qgemm_oracle as oc  # input generators only
     torch.cuda.set_device(0)
     n = args.launches
-    if args.case in ("cfg3", "cfg4", "cfg1"):
+    if args.case == "act_quant":  # --m rows (default 8192) of 8192 bf16 values
+        X = torch.randn((args.m or 8192, 8192), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda()
+        for _ in range(n):
+            C, _s = q.act_quant(X)
+    elif args.case in ("cfg3", "cfg4", "cfg1"):
         A, B, sa, sb = [t.cuda() for t in oc.make_config_inputs(args.case)]
         odt = "float16" if args.case == "cfg1" else "bfloat16"
         for _ in range(n):
@@ -446,7 +460,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-suite", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"], default=None,
+    ap.add_argument("--case", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "act_quant"], default=None,
                     help="profiling helper: launch one configuration a few times and exit")
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--launches", type=int, default=4)

@@ -168,6 +168,21 @@ int qgemm_unpack_int4(const uint8_t* B_packed, int8_t* out, int64_t N, int64_t K
 int qgemm_w4a8(const int8_t* A, const uint8_t* qB, int8_t* workspace, void* C, int64_t M, int64_t N, int64_t K,
                int signed_nibbles, int out_dtype, uint32_t* status, void* stream);
 
+/*
+ * Per-token activation quantiser, the step in front of the W8A8 GEMM: it produces that GEMM's A and scale_a.
+ * Replaces the compiled `call` of act_quant_kernel_int8_optimized (examples/deepseek_v4/act_quant.py:33-92)
+ * and follows its golden act_quant_torch (:112-142) bit for bit:
+ *
+ *   amax[m] = max(max_n |X[m,n]|, 1e-4)
+ *   S[m]    = amax[m] / 127                       (round_scale != 0: 2^ceil(log2(amax[m] / 127)))
+ *   Y[m,n]  = int8( round_half_even( clamp(X[m,n] / S[m], -127, 127) ) )
+ *
+ * X: [M, N] of x_dtype (F16 / BF16), 16-byte aligned.  Y: [M, N] int8.  S: [M] fp32.  Requires N % 8 == 0.
+ * A 3-D input [batch, seq, N] is the same call with M = batch * seq.
+ */
+int qgemm_act_quant(const void* X, int8_t* Y, float* S, int64_t M, int64_t N, int x_dtype, int round_scale,
+                    void* stream);
+
 #ifdef __cplusplus
 }
 #endif

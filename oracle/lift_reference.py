@@ -78,3 +78,8 @@ def w4a8():
 
 def two_scale_golden():
     return lift("examples/deepseek_v4/int8_gemm.py", ["int8_gemm_torch_optimized"])["int8_gemm_torch_optimized"]
+
+
+def act_quant_golden():
+    import typing
+    return lift("examples/deepseek_v4/act_quant.py", ["act_quant_torch"], {"Tuple": typing.Tuple})["act_quant_torch"]

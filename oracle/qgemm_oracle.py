@@ -245,6 +245,26 @@ def act_quant_ref(x: torch.Tensor):
     return q, scale.squeeze(1)
 
 
+def act_quant_torch_ref(x: torch.Tensor, round_scale: bool = False):
+    """Per-token int8 quantiser: x [M, N] or [batch, seq, N] -> (int8 like x, fp32 scales [..., 1]).
+
+    Follows the golden act_quant_torch of examples/deepseek_v4/act_quant.py:112-142 step by step:
+    ``amax = clamp(max|x|, min=1e-4)`` per row in fp32 (:126-128); ``scales = amax / 127`` or, with
+    ``round_scale``, ``2 ** ceil(log2(amax / 127))`` (:130-133); ``q = round(clamp(x / scales, -127, 127))``
+    cast through float16 to int8 (:135-137); 3-D inputs keep their shape and get scales [batch, seq, 1]
+    (:139-141).  (The recipe in examples/deepseek_v4/int8_gemm.py:143-151, restated in ``act_quant_ref``,
+    differs only in clamping to -128.)"""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1]).to(torch.float32)
+    amax = torch.clamp(x2.abs().amax(dim=1, keepdim=True), min=1e-4)
+    if round_scale:
+        scales = 2 ** torch.ceil(torch.log2(amax / 127.0))
+    else:
+        scales = amax / 127.0
+    q = torch.round(torch.clamp(x2 / scales, -127, 127)).to(torch.float16).to(torch.int8)
+    return q.reshape(shape), scales.reshape(tuple(shape[:-1]) + (1,))
+
+
 # ----------------------------------------------------------------------------
 # Seeded synthetic inputs for the five benchmark configurations
 # ----------------------------------------------------------------------------

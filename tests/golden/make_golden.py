@@ -120,6 +120,23 @@ def main():
     out["gen_quant4"] = dict(s=to_np(s), q_minus8=to_np(w_minus8.to(torch.int8)),
                              ref_weight_nk=to_np(linear.weight.data.contiguous()))
 
+    # --- per-token activation quantiser golden (examples/deepseek_v4/act_quant.py, seed 42) -------
+    aq = lr.act_quant_golden()
+    torch.manual_seed(42)
+    x = torch.randn(40, 1024, dtype=torch.bfloat16)
+    x[3] = 0  # an all-zero row exercises the 1e-4 floor
+    x[5] *= 1000.0
+    x[7, :512] = 0.5  # exact ties after scaling
+    x[7, 512:] = 127.0
+    y, s = aq(x, round_scale=False)
+    out["act_quant_2d"] = dict(x=to_np(x), y=to_np(y), s=to_np(s))
+    x3 = (torch.randn(2, 5, 256) * 3).to(torch.bfloat16)
+    y, s = aq(x3, round_scale=True)
+    out["act_quant_3d_round"] = dict(x=to_np(x3), y=to_np(y), s=to_np(s))
+    xh = torch.randn(6, 4104, dtype=torch.float16)
+    y, s = aq(xh, round_scale=False)
+    out["act_quant_f16"] = dict(x=to_np(xh), y=to_np(y), s=to_np(s))
+
     flat = {f"{case}/{key}": v for case, d in out.items() for key, v in d.items()}
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **flat)

@@ -127,3 +127,27 @@ def test_restatement_matches_live_reference():
     qu = lr.load_quantize_utils()
     v = torch.randint(0, 16, (4, 16), dtype=torch.int8, generator=g)
     assert torch.equal(oc.pack_uint4(v), qu.general_compress(v, 4, torch.uint8))
+
+
+ACT_QUANT_CASES = [("act_quant_2d", False, ("x",)), ("act_quant_3d_round", True, ("x",)), ("act_quant_f16", False, ())]
+
+
+@pytest.mark.parametrize("name,round_scale,bf16", ACT_QUANT_CASES)
+def test_act_quant_restatement_matches_reference_vectors(golden, name, round_scale, bf16):
+    """examples/deepseek_v4/act_quant.py:112-142 (golden act_quant_torch): int8 values and scales, bit for bit."""
+    c = golden.case(name, bf16=bf16)
+    y, s = oc.act_quant_torch_ref(c["x"], round_scale=round_scale)
+    assert torch.equal(y, c["y"])
+    assert torch.equal(s, c["s"])
+    assert y.shape == c["x"].shape and s.shape == tuple(c["x"].shape[:-1]) + (1,)
+
+
+@needs_ref
+def test_lifted_act_quant_equals_restatement():
+    ref = lr.act_quant_golden()
+    torch.manual_seed(7)
+    for shape, rs in (((33, 264), False), ((3, 4, 128), True), ((5, 72), True)):
+        x = (torch.randn(*shape) * 2).to(torch.bfloat16)
+        y0, s0 = ref(x, round_scale=rs)
+        y1, s1 = oc.act_quant_torch_ref(x, round_scale=rs)
+        assert torch.equal(y0, y1) and torch.equal(s0, s1)

@@ -5,6 +5,8 @@ The kernels are hand-written CUDA for sm_100a in ``csrc/`` and are reached throu
 ``libqgemm.so`` (``include/qgemm.h``).  There is no CPU or library fallback.
 """
 from .ops import (  # noqa: F401
+    act_quant,
+    act_quant_kernel_int8_optimized,
     dequant_gemm_fp16_wrapper,
     dequant_gemm_int8_wrapper,
     quant_matmul,

@@ -10,6 +10,7 @@
 
 #include "w4a16.cuh"
 #include "w4a16_decode.cuh"
+#include "act_quant.cuh"
 #include "w8a8.cuh"
 
 namespace {
@@ -479,6 +480,45 @@ int qgemm_unpack_int4(const uint8_t* B_packed, int8_t* out, int64_t N, int64_t K
   const long long grid = (threads + block - 1) / block;
   if (grid > 0x7fffffffll) return fail("qgemm_unpack_int4: tensor too large");
   unpack_int4_kernel<<<(unsigned)grid, block, 0, static_cast<cudaStream_t>(stream)>>>(B_packed, out, n_bytes, signed_nibbles);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int qgemm_act_quant(const void* X, int8_t* Y, float* S, int64_t M, int64_t N, int x_dtype, int round_scale,
+                    void* stream) {
+  if (M < 0 || N <= 0 || (N % 8) != 0) return fail("qgemm_act_quant: M >= 0 and N a positive multiple of 8 required (got M=%lld, N=%lld)", (long long)M, (long long)N);
+  if (N > (1ll << 30)) return fail("qgemm_act_quant: N too large (%lld)", (long long)N);
+  if (x_dtype != QGEMM_DT_F16 && x_dtype != QGEMM_DT_BF16) return fail("qgemm_act_quant: x_dtype must be F16 or BF16 (got %d)", x_dtype);
+  if (M == 0) return 0;
+  if (X == nullptr || Y == nullptr || S == nullptr) return fail("qgemm_act_quant: null pointer");
+  if (!aligned16(X) || (reinterpret_cast<uintptr_t>(Y) & 7u) != 0 || (reinterpret_cast<uintptr_t>(S) & 3u) != 0)
+    return fail("qgemm_act_quant: X must be 16-byte, Y 8-byte and S 4-byte aligned");
+  qg::ActQuantParams p;
+  p.X = static_cast<const uint4*>(X);
+  p.Y = Y;
+  p.S = S;
+  p.M = M;
+  p.N = (int)N;
+  p.is_bf16 = x_dtype == QGEMM_DT_BF16;
+  p.round_scale = round_scale != 0;
+  const int64_t chunks = N / 8;
+  // threads per row: the fewest of 32..256 that keep a row in at most 4 chunks per thread (8 at 256)
+  int tpr = 32;
+  while (tpr < qg::AQ_THREADS && chunks > (int64_t)tpr * 4) tpr *= 2;
+  const bool keep8 = chunks > (int64_t)tpr * 4;
+  const int64_t rows_per_block = qg::AQ_THREADS / tpr;
+  const int64_t grid = (M + rows_per_block - 1) / rows_per_block;
+  if (grid > 0x7fffffffll) return fail("qgemm_act_quant: too many rows (%lld)", (long long)M);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (tpr) {
+    case 32: qg::act_quant_kernel<32, 4><<<(unsigned)grid, qg::AQ_THREADS, 0, st>>>(p); break;
+    case 64: qg::act_quant_kernel<64, 4><<<(unsigned)grid, qg::AQ_THREADS, 0, st>>>(p); break;
+    case 128: qg::act_quant_kernel<128, 4><<<(unsigned)grid, qg::AQ_THREADS, 0, st>>>(p); break;
+    default:
+      if (keep8) qg::act_quant_kernel<256, qg::AQ_MAX_CHUNKS><<<(unsigned)grid, qg::AQ_THREADS, 0, st>>>(p);
+      else qg::act_quant_kernel<256, 4><<<(unsigned)grid, qg::AQ_THREADS, 0, st>>>(p);
+      break;
+  }
   CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -374,3 +374,52 @@ def dequant_gemm_int8_wrapper(M: int, N: int, K: int, block_M: int, block_N: int
         return C.cpu() if on_cpu else C
 
     return wrapper
+
+
+# --------------------------------------------------------------------------- per-token activation quantiser
+def act_quant(x, round_scale: bool = False, stream=None):
+    """bf16/f16 ``x`` [M, N] or [batch, seq, N] -> (int8 of the same shape, fp32 scales [M, 1] or [batch, seq, 1]).
+
+    Same arguments and results as the reference golden ``act_quant_torch(x, round_scale)``
+    (examples/deepseek_v4/act_quant.py:112-142), computed on the GPU: per row ``scale = max(amax, 1e-4) / 127``
+    (a power of two not below it when ``round_scale``), ``y = round(clamp(x / scale, -127, 127))``.  The
+    outputs are what ``quant_matmul`` takes as ``A`` and ``scale_a``."""
+    lib = _lib.load()
+    _require_cuda(x, "x")
+    dev = x.device
+    if x.dim() not in (2, 3):
+        raise ValueError(f"x must be 2-D or 3-D, got {x.dim()}-D")
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError(f"x must be bfloat16 or float16, got {x.dtype}")
+    if not x.is_contiguous():
+        raise ValueError("Input tensor at index 0 (x) must be contiguous")
+    N = x.shape[-1]
+    M = x.numel() // N if N else 0
+    y = torch.empty(x.shape, dtype=torch.int8, device=dev)
+    s = torch.empty(tuple(x.shape[:-1]) + (1,), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.qgemm_act_quant(x.data_ptr(), y.data_ptr(), s.data_ptr(), M, N,
+                                 _lib.DT_BF16 if x.dtype == torch.bfloat16 else _lib.DT_F16,
+                                 1 if round_scale else 0, _stream_handle(stream, dev))
+    _lib.check(rc, "qgemm_act_quant")
+    return y, s
+
+
+@functools.lru_cache(maxsize=None)
+def act_quant_kernel_int8_optimized(N: int, block_M: int = 32, block_N: int = 32, round_scale: bool = False):
+    """Factory with the signature of examples/deepseek_v4/act_quant.py:33.
+
+    Returns ``kernel(X[M, N] bf16) -> (Y[M, N] int8, S[M] fp32)`` with M free, as in the reference (:34,
+    outputs at ``out_idx=[-2, -1]``, :25); ``block_M`` / ``block_N`` are accepted as hints only."""
+    if N <= 0 or N % 8:
+        raise ValueError(f"N must be a positive multiple of 8, got {N}")
+    if block_M <= 0 or block_N <= 0:
+        raise ValueError("block_M and block_N must be positive")
+
+    def kernel(X, stream=None):
+        if X.dim() != 2 or X.shape[1] != N:
+            raise ValueError(f"X must have shape [M, {N}], got {tuple(X.shape)}")
+        y, s = act_quant(X, round_scale=round_scale, stream=stream)
+        return y, s.view(-1)
+
+    return kernel
