@@ -336,6 +336,27 @@ def run_suite(q, world, rank, peaks):
                 "tops": round(ops / ms / 1e9, 1), "frac_of_2x_measured_bf16": round(ops / ms / 1e9 / (world * int8_peak), 4)})
     del A, B
 
+    if world == 1:
+        # ragged form of config 4: 16 experts, the same 8192 tokens split unevenly (seeded), same K and N
+        Kg, Ng, G = 7168, 2048, 16
+        gen = torch.Generator().manual_seed(4)
+        w = torch.rand(G, generator=gen) + 0.2
+        sizes = (w / w.sum() * 8192).floor().to(torch.int64)
+        sizes[-1] += 8192 - int(sizes.sum())
+        sizes = [int(x) for x in sizes]
+        Ag = torch.randint(-128, 128, (8192, Kg), dtype=torch.int8, generator=gen).cuda()
+        Bg = torch.randint(-128, 128, (G, Kg, Ng), dtype=torch.int8, generator=gen).cuda()
+        sbg = (torch.rand((G, Ng), generator=gen) * 0.019 + 0.001).cuda()
+        sag = (torch.rand(8192, generator=gen) * 0.019 + 0.001).cuda()
+        meta = q.build_block_metadata(sizes, 128, "cuda")
+        Cg = torch.empty((8192, Ng), dtype=torch.bfloat16, device="cuda")
+        ms = _time_rotating(lambda i: q.grouped_quant_matmul(Ag, Bg, meta, sbg, sag, out_dtype="bfloat16", out=Cg), 1, 20, world)
+        ops = 2 * 8192 * Kg * Ng
+        res.append({"config": f"grouped W8A8, 16 ragged groups {min(sizes)}..{max(sizes)} rows (8192 total) x 7168 x 2048 bf16",
+                    "ms": round(ms, 5), "tops": round(ops / ms / 1e9, 1), "row_blocks": int(meta.shape[0]),
+                    "frac_of_2x_measured_bf16": round(ops / ms / 1e9 / int8_peak, 4)})
+        del Ag, Bg
+
     # config 5: weight columns sharded, all-gather of outputs; two weight copies so reads stay L2-cold
     K, N = 8192, 28672
     _, P, S = oc.make_config_inputs("cfg5", M=1)

@@ -81,6 +81,28 @@ int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const flo
                int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t scale_b_len,
                int64_t scale_a_len, int out_dtype, int b_layout, uint32_t* status, void* stream);
 
+/*
+ * Grouped (ragged) W8A8 matmul: row groups of different sizes, stacked in one A, each multiplied by its own
+ * B.  The quantized counterpart of the grouped GEMM of examples/grouped_gemm/example_grouped_gemm_fwd.py:44-113
+ * (same operands and the same host-built table; the int8 arithmetic and the scale epilogue are qgemm_w8a8's).
+ *
+ *   for every row block i = (g, m0, rows) of block_metadata and r < rows:
+ *     acc[m0+r, n] = sum_k int32(A[m0+r, k]) * int32(B[g, k, n])
+ *     C[m0+r, n]   = cast_out( float(acc) [* scale_a[m0+r]] * scale_b[g or 0, n] )
+ *
+ * A: [total_M, K] int8.  B: [groups, K, N] (QGEMM_B_KN) or [groups, N, K] (QGEMM_B_NK) int8.
+ * block_metadata: device int32 [num_blocks, 3] = (group index, first row in A / C, valid rows), as
+ *    construct_inputs builds it (example_grouped_gemm_fwd.py:147-166), with at most 128 rows per block.
+ *    Unlike the reference kernel (README.md:16-22) partial blocks are allowed: only `rows` rows are written.
+ *    Rows of C that no block covers are left untouched.  An entry that points outside the tensors is skipped.
+ * scale_b: fp32, scale_b_len = 1, N or groups*N.  scale_a: nullable fp32 [total_M].  C, acc_out, out_dtype,
+ * b_layout, status, stream as qgemm_w8a8.  Requires K % 16 == 0 and N % 16 == 0.
+ */
+int qgemm_w8a8_grouped(const int8_t* A, const int8_t* B, const float* scale_b, const float* scale_a, void* C,
+                       int32_t* acc_out, const int32_t* block_metadata, int64_t num_blocks, int64_t groups,
+                       int64_t total_M, int64_t N, int64_t K, int64_t scale_b_len, int64_t scale_a_len, int out_dtype,
+                       int b_layout, uint32_t* status, void* stream);
+
 /* Bytes of scratch memory qgemm_w4a16 needs for this problem on the current device (split-K partial
  * sums and arrival counters).  The first use of a scratch buffer must find its first
  * qgemm_w4a16_counter_bytes() bytes zeroed; the kernel leaves them zero.  Two launches that may

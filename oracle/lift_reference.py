@@ -83,3 +83,7 @@ def two_scale_golden():
 def act_quant_golden():
     import typing
     return lift("examples/deepseek_v4/act_quant.py", ["act_quant_torch"], {"Tuple": typing.Tuple})["act_quant_torch"]
+
+
+def grouped_gemm_reference():
+    return lift("examples/grouped_gemm/example_grouped_gemm_fwd.py", ["torch_gmm", "construct_inputs"])

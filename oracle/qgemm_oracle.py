@@ -245,6 +245,39 @@ def act_quant_ref(x: torch.Tensor):
     return q, scale.squeeze(1)
 
 
+def build_block_metadata_ref(batch_sizes_list, block_M):
+    """(group, first row, valid rows) per row block, as construct_inputs builds it in
+    examples/grouped_gemm/example_grouped_gemm_fwd.py:147-166."""
+    rows, off = [], 0
+    for g, size in enumerate(batch_sizes_list):
+        for i in range((size + block_M - 1) // block_M):
+            rows.append([g, off + i * block_M, min(block_M, size - i * block_M)])
+        off += size
+    return torch.tensor(rows, dtype=torch.int32).reshape(-1, 3)
+
+
+def grouped_quant_matmul_ref(A, B, block_metadata, scale, out_dtype, scale_a=None, b_layout="KN", return_acc=False):
+    """Ragged grouped W8A8 reference: the block loop of torch_gmm
+    (examples/grouped_gemm/example_grouped_gemm_fwd.py:7-41) with the W8A8 arithmetic of ``quant_matmul_ref``
+    per block: ``out[m0:m0+rows] = cast(int32(A[m0:m0+rows] @ B[g]) [* scale_a] * scale[g or 0])``.
+
+    A [total_M, K] int8; B [G, K, N] (or [G, N, K] with ``b_layout="NK"``, torch_gmm's ``trans_b``, :33-34);
+    scale fp32 [1], [N] or [G, N]; scale_a fp32 [total_M] or None.  Rows no block covers stay zero."""
+    out_dtype = _dt(out_dtype)
+    G = B.shape[0]
+    N = B.shape[2] if b_layout == "KN" else B.shape[1]
+    out = torch.zeros((A.shape[0], N), dtype=out_dtype)
+    acc = torch.zeros((A.shape[0], N), dtype=torch.int32)
+    for g, m0, rows in block_metadata.cpu().tolist():
+        part_b = B[g] if b_layout == "KN" else B[g].transpose(0, 1)
+        sc = scale[g] if scale.dim() == 2 and scale.shape[0] == G else scale
+        sa = None if scale_a is None else scale_a[m0:m0 + rows]
+        c, a32 = quant_matmul_ref(A[m0:m0 + rows], part_b.contiguous(), sc.reshape(-1), out_dtype, scale_a=sa, return_acc=True)
+        out[m0:m0 + rows] = c
+        acc[m0:m0 + rows] = a32
+    return (out, acc) if return_acc else out
+
+
 def act_quant_torch_ref(x: torch.Tensor, round_scale: bool = False):
     """Per-token int8 quantiser: x [M, N] or [batch, seq, N] -> (int8 like x, fp32 scales [..., 1]).
 

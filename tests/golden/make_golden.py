@@ -137,6 +137,21 @@ def main():
     y, s = aq(xh, round_scale=False)
     out["act_quant_f16"] = dict(x=to_np(xh), y=to_np(y), s=to_np(s))
 
+    # --- grouped GEMM block loop and table (examples/grouped_gemm/example_grouped_gemm_fwd.py), seed 0 ----
+    # torch_gmm on integer-valued int32 operands gives the exact accumulators of the quantized form; the
+    # table comes from construct_inputs with the reference's own block_M (ragged sizes, one empty tail block).
+    gg = lr.grouped_gemm_reference()
+    torch.manual_seed(0)
+    sizes, K, N, bm = [63, 77, 111, 280], 96, 48, 64
+    _, _, meta = gg["construct_inputs"](sizes, K, N, False, bm, "cpu", torch.float32)
+    A = torch.randint(-128, 127, [sum(sizes), K], dtype=torch.int8)
+    B = torch.randint(-128, 127, [len(sizes), K, N], dtype=torch.int8)
+    acc = gg["torch_gmm"](A.to(torch.int32), B.to(torch.int32), meta)
+    acc_t = gg["torch_gmm"](A.to(torch.int32), B.transpose(1, 2).contiguous().to(torch.int32), meta, trans_b=True)
+    assert torch.equal(acc, acc_t)
+    out["grouped_gemm"] = dict(sizes=np.array(sizes, dtype=np.int64), block_M=np.array([bm], dtype=np.int64),
+                               A=to_np(A), B=to_np(B), meta=to_np(meta), acc=to_np(acc))
+
     flat = {f"{case}/{key}": v for case, d in out.items() for key, v in d.items()}
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **flat)

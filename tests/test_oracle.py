@@ -151,3 +151,23 @@ def test_lifted_act_quant_equals_restatement():
         y0, s0 = ref(x, round_scale=rs)
         y1, s1 = oc.act_quant_torch_ref(x, round_scale=rs)
         assert torch.equal(y0, y1) and torch.equal(s0, s1)
+
+
+def test_grouped_gemm_restatement_matches_reference_vectors(golden):
+    """examples/grouped_gemm/example_grouped_gemm_fwd.py: the table of construct_inputs (:147-166) and the block
+    loop of torch_gmm (:7-41) on integer operands = the exact accumulators of the grouped W8A8 form."""
+    c = golden.case("grouped_gemm")
+    sizes, bm = c["sizes"].tolist(), int(c["block_M"][0])
+    assert torch.equal(oc.build_block_metadata_ref(sizes, bm), c["meta"])
+    one = torch.ones(1)
+    _, acc = oc.grouped_quant_matmul_ref(c["A"], c["B"], c["meta"], one, "float16", return_acc=True)
+    assert torch.equal(acc, c["acc"])
+    _, acc_t = oc.grouped_quant_matmul_ref(c["A"], c["B"].transpose(1, 2).contiguous(), c["meta"], one, "float16",
+                                           b_layout="NK", return_acc=True)
+    assert torch.equal(acc_t, c["acc"])
+
+
+def test_block_metadata_builder_matches_oracle():
+    import tilelang_ascend_b200.ops as ops
+    for sizes, bm in (([64], 64), ([63, 77, 111, 280], 64), ([100, 0, 300, 5], 128), ([], 128)):
+        assert torch.equal(ops.build_block_metadata(sizes, bm), oc.build_block_metadata_ref(sizes, bm))

@@ -7,6 +7,9 @@ The kernels are hand-written CUDA for sm_100a in ``csrc/`` and are reached throu
 from .ops import (  # noqa: F401
     act_quant,
     act_quant_kernel_int8_optimized,
+    build_block_metadata,
+    grouped_quant_gemm,
+    grouped_quant_matmul,
     dequant_gemm_fp16_wrapper,
     dequant_gemm_int8_wrapper,
     quant_matmul,

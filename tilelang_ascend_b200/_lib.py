@@ -31,6 +31,9 @@ SIGNATURES = {
     "qgemm_w8a8": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                               _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
                               _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
+    "qgemm_w8a8_grouped": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                      _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
+                                      _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
     "qgemm_w4a16_workspace_bytes": (_c.c_int64, [_c.c_int64, _c.c_int64, _c.c_int64]),
     "qgemm_w4a16_counter_bytes": (_c.c_int64, []),
     "qgemm_w4a16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p,

@@ -244,9 +244,13 @@ int qgemm_init(void) {
   return ensure_device(&sms);
 }
 
-int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const float* scale_a, void* C,
-               int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t scale_b_len,
-               int64_t scale_a_len, int out_dtype, int b_layout, uint32_t* status, void* stream) {
+// Plain / batched form: meta == nullptr.  Grouped form: A and C are single [M, K] / [M, N] stacks, B holds
+// `batch` (= groups) matrices and `meta` lists num_blocks row blocks (group, first row, valid rows).
+static int w8a8_impl(const int8_t* A, const int8_t* B, const float* scale_b, const float* scale_a, void* C,
+                     int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t scale_b_len,
+                     int64_t scale_a_len, int out_dtype, int b_layout, uint32_t* status, void* stream,
+                     const int* meta, int64_t num_blocks) {
+  const int64_t batchA = meta ? 1 : batch;  // batch extent of A, C and scale_a
   if (batch <= 0 || M <= 0 || N <= 0 || K <= 0) return fail("qgemm_w8a8: batch, M, N, K must be positive (got %lld, %lld, %lld, %lld)", (long long)batch, (long long)M, (long long)N, (long long)K);
   if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30) || batch > 65535) return fail("qgemm_w8a8: dimension too large");
   if (A == nullptr || B == nullptr) return fail("qgemm_w8a8: A and B must not be null");
@@ -261,7 +265,7 @@ int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const flo
     if (C != nullptr) {
       if (scale_b == nullptr) return fail("qgemm_w8a8: scale_b must not be null");
       if (scale_b_len != 1 && scale_b_len != N && scale_b_len != batch * N) return fail("qgemm_w8a8: scale_b_len must be 1, N or batch*N (got %lld)", (long long)scale_b_len);
-      if (scale_a != nullptr && scale_a_len != M && scale_a_len != batch * M) return fail("qgemm_w8a8: scale_a_len must be M or batch*M (got %lld)", (long long)scale_a_len);
+      if (scale_a != nullptr && scale_a_len != M && scale_a_len != batchA * M) return fail("qgemm_w8a8: scale_a_len must be M or batch*M (got %lld)", (long long)scale_a_len);
     }
   } else {
     return fail("qgemm_w8a8: out_dtype must be F16, BF16 or I32 (got %d)", out_dtype);
@@ -274,12 +278,13 @@ int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const flo
 
   CUtensorMap tmA, tmB;
   {
-    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)batch};
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)batchA};
     const uint64_t str[2] = {(uint64_t)K, (uint64_t)M * (uint64_t)K};
     const uint32_t box[3] = {128, 128, 1};
     if (encode_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, A, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
   }
-  const int64_t tiles256 = batch * ((M + 127) / 128) * ((N + 255) / 256);
+  const int64_t m_tiles = meta ? num_blocks : (M + 127) / 128;
+  const int64_t tiles256 = batchA * m_tiles * ((N + 255) / 256);
   const int BN = (N > 128 && tiles256 >= sms) ? 256 : 128;
   // Width actually computed per tile (a multiple of 32, at most BN).  Narrower tiles that fill the last
   // round of the persistent grid better were measured slower on B200 (224 instead of 256 columns on the
@@ -288,7 +293,7 @@ int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const flo
   // Pairs of CTAs on 256 x 256 tiles when there is at least one tile per pair and M fills both halves.
   const int64_t pair_tiles = batch * ((M + 255) / 256) * ((N + 255) / 256);
   static const int pair_mode = getenv("QGEMM_W8_PAIR") ? atoi(getenv("QGEMM_W8_PAIR")) : 0;
-  const bool use_pair = pair_mode != 0 && M >= 256 && N >= 256 && pair_tiles >= sms / 2;
+  const bool use_pair = meta == nullptr && pair_mode != 0 && M >= 256 && N >= 256 && pair_tiles >= sms / 2;
   if (b_layout == QGEMM_B_KN) {
     const uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)batch};
     const uint64_t str[2] = {(uint64_t)N, (uint64_t)K * (uint64_t)N};
@@ -306,16 +311,18 @@ int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const flo
   p.scale_a = scale_a;
   p.C = C;
   p.acc_out = acc_out;
-  p.batch = (int)batch;
+  p.batch = (int)batchA;
+  p.meta = meta;
+  p.groups = (int)batch;
   p.M = (int)M;
   p.N = (int)N;
   p.K = (int)K;
   p.sb_mode = (scale_b_len == 1) ? 0 : ((scale_b_len == N) ? 1 : 2);
   p.sa_mode = (scale_a == nullptr) ? 0 : ((scale_a_len == M) ? 1 : 2);
-  p.m_tiles = (int)((M + 127) / 128);
+  p.m_tiles = (int)m_tiles;
   p.n_tiles = (int)((N + bn_eff - 1) / bn_eff);
   p.bn = bn_eff;
-  const int64_t num_tiles = batch * p.m_tiles * p.n_tiles;
+  const int64_t num_tiles = batchA * p.m_tiles * p.n_tiles;
   if (num_tiles > 0x7fffffff) return fail("qgemm_w8a8: too many tiles");
   p.num_tiles = (int)num_tiles;
   p.k_blocks = (int)((K + 127) / 128);
@@ -341,6 +348,26 @@ int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const flo
   }
   if (nk) return bf ? launch_w8<128, true, true>(tmA, tmB, p, grid, s) : launch_w8<128, true, false>(tmA, tmB, p, grid, s);
   return bf ? launch_w8<128, false, true>(tmA, tmB, p, grid, s) : launch_w8<128, false, false>(tmA, tmB, p, grid, s);
+}
+
+int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const float* scale_a, void* C,
+               int32_t* acc_out, int64_t batch, int64_t M, int64_t N, int64_t K, int64_t scale_b_len,
+               int64_t scale_a_len, int out_dtype, int b_layout, uint32_t* status, void* stream) {
+  return w8a8_impl(A, B, scale_b, scale_a, C, acc_out, batch, M, N, K, scale_b_len, scale_a_len, out_dtype, b_layout,
+                   status, stream, nullptr, 0);
+}
+
+int qgemm_w8a8_grouped(const int8_t* A, const int8_t* B, const float* scale_b, const float* scale_a, void* C,
+                       int32_t* acc_out, const int32_t* block_metadata, int64_t num_blocks, int64_t groups,
+                       int64_t total_M, int64_t N, int64_t K, int64_t scale_b_len, int64_t scale_a_len, int out_dtype,
+                       int b_layout, uint32_t* status, void* stream) {
+  if (num_blocks < 0) return fail("qgemm_w8a8_grouped: num_blocks must not be negative (got %lld)", (long long)num_blocks);
+  if (num_blocks == 0 || total_M == 0) return 0;  // no rows: nothing to compute
+  if (block_metadata == nullptr) return fail("qgemm_w8a8_grouped: block_metadata must not be null");
+  if ((reinterpret_cast<uintptr_t>(block_metadata) & 3u) != 0) return fail("qgemm_w8a8_grouped: block_metadata must be 4-byte aligned");
+  if (num_blocks > (1ll << 24)) return fail("qgemm_w8a8_grouped: too many row blocks (%lld)", (long long)num_blocks);
+  return w8a8_impl(A, B, scale_b, scale_a, C, acc_out, groups, total_M, N, K, scale_b_len, scale_a_len, out_dtype,
+                   b_layout, status, stream, block_metadata, num_blocks);
 }
 
 int64_t qgemm_w4a16_counter_bytes(void) { return kW4CounterBytes; }

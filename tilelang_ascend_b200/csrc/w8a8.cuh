@@ -25,6 +25,15 @@ struct W8A8Params {
   int bn;            // columns per tile actually computed: a multiple of 32, at most the kernel's BN
   uint32_t* status;  // nullable device word
   unsigned long long wait_limit_ns;
+  // Grouped (ragged) form: A and C are [M, K] / [M, N] stacks of row groups, B is [groups, ...]; row block i
+  // of the table is (group, first row, valid rows <= 128).  Null for the plain and batched forms.
+  const int* meta;
+  int groups;
+};
+
+// One output tile's coordinates: batch index of B / scale_b, batch index of A / C / scale_a, first row, valid rows.
+struct W8Tile {
+  int bB, bA, m0, rows, n_blk;
 };
 
 constexpr int W8_BM = 128;      // tile rows (= MMA M, one TMEM lane per row)
@@ -55,6 +64,27 @@ __device__ __forceinline__ void w8_decode_tile(const W8A8Params& p, int tile, in
   const int in_band = r - g * band;
   m_blk = first_m + in_band % gsz;
   n_blk = in_band / gsz;
+}
+
+__device__ __forceinline__ W8Tile w8_tile(const W8A8Params& p, int tile) {
+  int b, m_blk, n_blk;
+  w8_decode_tile(p, tile, b, m_blk, n_blk);
+  W8Tile t;
+  t.n_blk = n_blk;
+  if (p.meta == nullptr) {
+    t.bB = t.bA = b;
+    t.m0 = m_blk * W8_BM;
+    t.rows = min(W8_BM, p.M - t.m0);
+  } else {
+    t.bB = __ldg(p.meta + 3 * m_blk);
+    t.bA = 0;
+    t.m0 = __ldg(p.meta + 3 * m_blk + 1);
+    t.rows = min(__ldg(p.meta + 3 * m_blk + 2), W8_BM);
+    // a table entry that points outside the tensors computes nothing (loads are bounds-checked by TMA)
+    if (t.bB < 0 || t.bB >= p.groups || t.m0 < 0 || t.m0 >= p.M) { t.bB = 0; t.m0 = 0; t.rows = 0; }
+    t.rows = min(t.rows, p.M - t.m0);
+  }
+  return t;
 }
 
 template <int BN, bool B_NK, bool OUT_BF16>
@@ -110,21 +140,20 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-        int b, m_blk, n_blk;
-        w8_decode_tile(p, tile, b, m_blk, n_blk);
-        const int m0 = m_blk * W8_BM, n0 = n_blk * p.bn;
+        const W8Tile t = w8_tile(p, tile);
+        const int m0 = t.m0, n0 = t.n_blk * p.bn;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           uint8_t* sA = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sB = sA + Cfg::A_BYTES;
           mbar_arrive_expect_tx(&full[stage], Cfg::STAGE_BYTES);
-          tma_load_3d(sA, &tmA, &full[stage], kb * W8_BK, m0, b);
+          tma_load_3d(sA, &tmA, &full[stage], kb * W8_BK, m0, t.bA);
           if constexpr (B_NK) {
-            tma_load_3d(sB, &tmB, &full[stage], kb * W8_BK, n0, b);
+            tma_load_3d(sB, &tmB, &full[stage], kb * W8_BK, n0, t.bB);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 128; ++c)
-              tma_load_3d(sB + c * (W8_BK * 128), &tmB, &full[stage], n0 + c * 128, kb * W8_BK, b);
+              tma_load_3d(sB + c * (W8_BK * 128), &tmB, &full[stage], n0 + c * 128, kb * W8_BK, t.bB);
           }
           issued_mask |= 1u << stage;
           parity_mask = (parity_mask & ~(1u << stage)) | (phase << stage);
@@ -195,18 +224,18 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     int it = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
-      int b, m_blk, n_blk;
-      w8_decode_tile(p, tile, b, m_blk, n_blk);
+      const W8Tile t = w8_tile(p, tile);
+      const int n_blk = t.n_blk;
       const int buf = it & 1;
       const uint32_t tphase = (it >> 1) & 1;
       if (!mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE)) break;
       tc_fence_after_sync();
-      const int m = m_blk * W8_BM + q * 32 + lane;
-      const bool row_ok = m < p.M;
+      const int m = t.m0 + q * 32 + lane;
+      const bool row_ok = q * 32 + lane < t.rows;
       float sa = 1.0f;
-      if (p.sa_mode != 0 && row_ok) sa = __ldg(p.scale_a + (p.sa_mode == 2 ? (size_t)b * p.M : 0) + m);
-      const float* sbp = p.scale_b + (p.sb_mode == 2 ? (size_t)b * p.N : 0);
-      const size_t row_off = ((size_t)b * p.M + (row_ok ? m : 0)) * (size_t)p.N;
+      if (p.sa_mode != 0 && row_ok) sa = __ldg(p.scale_a + (p.sa_mode == 2 ? (size_t)t.bA * p.M : 0) + m);
+      const float* sbp = p.scale_b + (p.sb_mode == 2 ? (size_t)t.bB * p.N : 0);
+      const size_t row_off = ((size_t)t.bA * p.M + (row_ok ? m : 0)) * (size_t)p.N;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
       const int chunks = p.bn >> 5;
 #pragma unroll 1

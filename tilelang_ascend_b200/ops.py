@@ -423,3 +423,112 @@ def act_quant_kernel_int8_optimized(N: int, block_M: int = 32, block_N: int = 32
         return y, s.view(-1)
 
     return kernel
+
+
+# --------------------------------------------------------------------------- grouped (ragged) W8A8
+def build_block_metadata(batch_sizes_list, block_M: int = 128, device=None):
+    """Row-block table [total_blocks, 3] int32 = (group, first row, valid rows) for stacked row groups.
+
+    The same table as ``construct_inputs`` builds on the host in
+    examples/grouped_gemm/example_grouped_gemm_fwd.py:147-166: blocks never cross a group boundary, the last
+    block of a group may be partial.  Empty groups contribute no block."""
+    if not isinstance(block_M, int) or block_M <= 0:
+        raise ValueError(f"block_M must be a positive integer, got {block_M!r}")
+    rows, off = [], 0
+    for g, size in enumerate(batch_sizes_list):
+        size = int(size)
+        if size < 0:
+            raise ValueError(f"group sizes must not be negative, got {size}")
+        for start in range(0, size, block_M):
+            rows.append((g, off + start, min(block_M, size - start)))
+        off += size
+    meta = torch.tensor(rows, dtype=torch.int32).reshape(-1, 3)
+    return meta if device is None else meta.to(device)
+
+
+def grouped_quant_matmul(A, B, block_metadata, scale, scale_a=None, out_dtype=torch.float16, b_layout="KN",
+                         stream=None, return_accumulators=False, status=None, out=None):
+    """Ragged grouped W8A8: for every table row (g, m0, rows): ``C[m0:m0+rows] = cast(int32(A[m0:m0+rows] @ B[g])
+    [* scale_a[m0:m0+rows, None]] * scale[g or 0])``.
+
+    A: [total_M, K] int8; B: [G, K, N] (``"KN"``) or [G, N, K] (``"NK"``) int8; block_metadata: CUDA int32
+    [blocks, 3] with at most 128 rows per block; scale: fp32 [1], [N] or [G, N]; scale_a: optional fp32 [total_M].
+    Rows of the result that no block covers keep the contents of ``out`` (zeros when ``out`` is not given)."""
+    lib = _lib.load()
+    _require_cuda(A, "A")
+    dev = A.device
+    out_dtype = _dt(out_dtype)
+    if A.dim() != 2 or B.dim() != 3:
+        raise ValueError("A must be 2-D [total_M, K] and B 3-D [G, K, N] or [G, N, K]")
+    total_M, K = A.shape
+    G = B.shape[0]
+    if b_layout == "KN":
+        N, b_shape = B.shape[2], (G, K, B.shape[2])
+    elif b_layout == "NK":
+        N, b_shape = B.shape[1], (G, B.shape[1], K)
+    else:
+        raise ValueError("b_layout must be 'KN' or 'NK'")
+    _check_tensor(A, 0, "A", torch.int8, None, dev)
+    _check_tensor(B, 1, "B", torch.int8, b_shape, dev)
+    _check_tensor(block_metadata, 2, "block_metadata", torch.int32, None, dev)
+    if block_metadata.dim() != 2 or block_metadata.shape[1] != 3:
+        raise ValueError(f"Static shape mismatch for parameter block_metadata: expected [blocks, 3], got {tuple(block_metadata.shape)}")
+    sb_len = sa_len = 0
+    if out_dtype != torch.int32:
+        _check_tensor(scale, 3, "scale", torch.float32, None, dev)
+        sb_len = scale.numel()
+        if sb_len not in (1, N, G * N):
+            raise ValueError(f"Static shape mismatch for parameter scale: expected [1], [{N}] or [{G}, {N}], got {tuple(scale.shape)}")
+        if scale_a is not None:
+            _check_tensor(scale_a, 4, "scale_a", torch.float32, None, dev)
+            sa_len = scale_a.numel()
+            if sa_len != total_M:
+                raise ValueError(f"Static shape mismatch for parameter scale_a: expected [{total_M}], got {tuple(scale_a.shape)}")
+    elif out_dtype not in _ABI_DT:
+        raise ValueError(f"unsupported out_dtype {out_dtype}")
+    if out is None:
+        C = torch.zeros((total_M, N), dtype=out_dtype, device=dev)
+    else:
+        _check_tensor(out, 5, "out", out_dtype, (total_M, N), dev)
+        C = out
+    acc = torch.zeros((total_M, N), dtype=torch.int32, device=dev) if (return_accumulators and out_dtype != torch.int32) else None
+    with torch.cuda.device(dev):
+        rc = lib.qgemm_w8a8_grouped(A.data_ptr(), B.data_ptr(), _ptr(scale) if out_dtype != torch.int32 else None,
+                                    _ptr(scale_a) if out_dtype != torch.int32 else None, C.data_ptr(), _ptr(acc),
+                                    block_metadata.data_ptr(), block_metadata.shape[0], G, total_M, N, K, sb_len,
+                                    sa_len, _ABI_DT[out_dtype], _lib.B_KN if b_layout == "KN" else _lib.B_NK,
+                                    _ptr(status), _stream_handle(stream, dev))
+    _lib.check(rc, "qgemm_w8a8_grouped")
+    if acc is not None:
+        return C, acc
+    return C
+
+
+@functools.lru_cache(maxsize=None)
+def grouped_quant_gemm(batch_sizes_list, K: int, N: int, block_M: int = 128, block_N: int = 256, block_K: int = 128,
+                       out_dtype="float16", b_layout: str = "KN"):
+    """Factory with the signature of ``grouped_gemm`` in examples/grouped_gemm/example_grouped_gemm_fwd.py:44,
+    for int8 operands: returns ``kernel(A, B, block_metadata, scale[, scale_a]) -> C``.
+
+    ``batch_sizes_list`` (a tuple, as the reference passes it, :174) fixes total_M and the group count;
+    ``block_M`` is the row-block height the caller's table was built with and must not exceed 128 (one tile);
+    ``block_N`` / ``block_K`` are hints.  ``kernel.block_metadata(device)`` returns the table for these sizes."""
+    sizes = tuple(int(x) for x in batch_sizes_list)
+    _check_blocks(block_M, block_N, block_K)
+    if block_M > 128:
+        raise ValueError(f"block_M must not exceed 128 rows (one output tile), got {block_M}")
+    total_M, G = sum(sizes), len(sizes)
+    blocks = sum((x + block_M - 1) // block_M for x in sizes)
+
+    def kernel(A, B, block_metadata, scale, scale_a=None, stream=None, return_accumulators=False):
+        if A.dim() != 2 or tuple(A.shape) != (total_M, K):
+            raise ValueError(f"Static shape mismatch for parameter A: expected ({total_M}, {K}), got {tuple(A.shape)}")
+        if B.dim() != 3 or B.shape[0] != G:
+            raise ValueError(f"Static shape mismatch for parameter B: expected {G} groups, got {tuple(B.shape)}")
+        if block_metadata.dim() != 2 or block_metadata.shape[0] != blocks:
+            raise ValueError(f"Static shape mismatch for parameter block_metadata: expected ({blocks}, 3), got {tuple(block_metadata.shape)}")
+        return grouped_quant_matmul(A, B, block_metadata, scale, scale_a, out_dtype=out_dtype, b_layout=b_layout,
+                                    stream=stream, return_accumulators=return_accumulators)
+
+    kernel.block_metadata = lambda device="cuda": build_block_metadata(sizes, block_M, device)
+    return kernel
