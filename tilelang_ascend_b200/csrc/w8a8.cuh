@@ -50,7 +50,8 @@ struct W8Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  static constexpr int SCALE_BYTES = 4 * BN * 4;  // each epilogue warp's copy of the tile's column scales
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + SCALE_BYTES + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ void w8_decode_tile(const W8A8Params& p, int tile, int& b, int& m_blk, int& n_blk) {
@@ -221,55 +222,76 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else {
     // ---------------------------------------------------------------- epilogue
+    // Each warp stages the tile's column scales in its own piece of shared memory BEFORE it waits for the
+    // accumulators (the loads hide behind the main loop), and keeps the next 32-column chunk's tcgen05.ld in
+    // flight while it converts and stores the current one.
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    float* sb_s = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES) + q * BN;
     int it = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const W8Tile t = w8_tile(p, tile);
       const int n_blk = t.n_blk;
       const int buf = it & 1;
       const uint32_t tphase = (it >> 1) & 1;
-      if (!mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE)) break;
-      tc_fence_after_sync();
       const int m = t.m0 + q * 32 + lane;
       const bool row_ok = q * 32 + lane < t.rows;
       float sa = 1.0f;
       if (p.sa_mode != 0 && row_ok) sa = __ldg(p.scale_a + (p.sa_mode == 2 ? (size_t)t.bA * p.M : 0) + m);
-      const float* sbp = p.scale_b + (p.sb_mode == 2 ? (size_t)t.bB * p.N : 0);
+      if (p.C != nullptr) {
+        const float* sbp = p.scale_b + (p.sb_mode == 2 ? (size_t)t.bB * p.N : 0);
+        __syncwarp();  // the previous tile's reads of sb_s are done
+        for (int c = lane; c < p.bn; c += 32) {
+          const int n = n_blk * p.bn + c;
+          sb_s[c] = (p.sb_mode == 0) ? __ldg(sbp) : (n < p.N ? __ldg(sbp + n) : 0.f);
+        }
+        __syncwarp();
+      }
+      if (!mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after_sync();
       const size_t row_off = ((size_t)t.bA * p.M + (row_ok ? m : 0)) * (size_t)p.N;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
       const int chunks = p.bn >> 5;
+      uint32_t r[2][32];
+      tmem_ld_32x32b_x32(taddr, r[0]);
 #pragma unroll 1
-      for (int c = 0; c < chunks; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int n = n_blk * p.bn + c * 32;
-        if (row_ok && n < p.N) {
-          if (p.acc_out != nullptr) {
-            int4* dst = reinterpret_cast<int4*>(p.acc_out + row_off + n);
+      for (int c2 = 0; c2 < chunks; c2 += 2) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (n + 4 * j < p.N) dst[j] = make_int4((int)r[4 * j], (int)r[4 * j + 1], (int)r[4 * j + 2], (int)r[4 * j + 3]);
-          }
-          uint16_t* cbase = reinterpret_cast<uint16_t*>(p.C) + row_off + n;
+        for (int h = 0; h < 2; ++h) {
+          const int c = c2 + h;
+          if (c >= chunks) break;
+          tmem_ld_wait();                                                     // chunk c is in r[h]
+          if (c + 1 < chunks) tmem_ld_32x32b_x32(taddr + (c + 1) * 32, r[h ^ 1]);  // chunk c + 1 in flight
+          const int n = n_blk * p.bn + c * 32;
+          if (row_ok && n < p.N) {
+            if (p.acc_out != nullptr) {
+              int4* dst = reinterpret_cast<int4*>(p.acc_out + row_off + n);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (p.C != nullptr && n + 8 * j < p.N) {
-              uint32_t o[4];
+              for (int j = 0; j < 8; ++j)
+                if (n + 4 * j < p.N)
+                  dst[j] = make_int4((int)r[h][4 * j], (int)r[h][4 * j + 1], (int)r[h][4 * j + 2], (int)r[h][4 * j + 3]);
+            }
+            if (p.C != nullptr) {
+              uint16_t* cbase = reinterpret_cast<uint16_t*>(p.C) + row_off + n;
+              const float4* sv = reinterpret_cast<const float4*>(sb_s + c * 32);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int col = 8 * j + 2 * e;
-                float s0, s1;
-                if (p.sb_mode == 0) { s0 = s1 = __ldg(sbp); }
-                else { s0 = __ldg(sbp + n + col); s1 = __ldg(sbp + n + col + 1); }
-                float f0 = __int2float_rn((int)r[col]);
-                float f1 = __int2float_rn((int)r[col + 1]);
-                if (p.sa_mode != 0) { f0 = __fmul_rn(f0, sa); f1 = __fmul_rn(f1, sa); }
-                f0 = __fmul_rn(f0, s0);
-                f1 = __fmul_rn(f1, s1);
-                o[e] = pack_out2<OUT_BF16>(f0, f1);
+              for (int j = 0; j < 4; ++j) {
+                if (n + 8 * j < p.N) {
+                  const float4 s_lo = sv[2 * j], s_hi = sv[2 * j + 1];
+                  const float sc[8] = {s_lo.x, s_lo.y, s_lo.z, s_lo.w, s_hi.x, s_hi.y, s_hi.z, s_hi.w};
+                  uint32_t o[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const int col = 8 * j + 2 * e;
+                    float f0 = __int2float_rn((int)r[h][col]);
+                    float f1 = __int2float_rn((int)r[h][col + 1]);
+                    if (p.sa_mode != 0) { f0 = __fmul_rn(f0, sa); f1 = __fmul_rn(f1, sa); }
+                    f0 = __fmul_rn(f0, sc[2 * e]);
+                    f1 = __fmul_rn(f1, sc[2 * e + 1]);
+                    o[e] = pack_out2<OUT_BF16>(f0, f1);
+                  }
+                  *reinterpret_cast<uint4*>(cbase + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
               }
-              *reinterpret_cast<uint4*>(cbase + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
             }
           }
         }
