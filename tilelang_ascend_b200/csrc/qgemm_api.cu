@@ -132,8 +132,9 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* b
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <int BN, bool NK, bool BF>
-int launch_w8(const CUtensorMap& tmA, const CUtensorMap& tmB, const qg::W8A8Params& p, int grid, cudaStream_t s) {
-  qg::w8a8_gemm_kernel<BN, NK, BF><<<grid, qg::W8_THREADS, qg::W8Cfg<BN>::SMEM_BYTES, s>>>(tmA, tmB, p);
+int launch_w8(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const qg::W8A8Params& p, int grid,
+              cudaStream_t s) {
+  qg::w8a8_gemm_kernel<BN, NK, BF><<<grid, qg::W8_THREADS, qg::W8Cfg<BN>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
   CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -306,7 +307,18 @@ static int w8a8_impl(const int8_t* A, const int8_t* B, const float* scale_b, con
     if (encode_map(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
   }
 
+  // C as a tensor map for the epilogue's tiled stores: boxes of 64 outputs x 32 rows, 128-byte swizzle.
+  CUtensorMap tmC = tmA;
+  const bool tma_store = C != nullptr && (bn_eff % 64) == 0;
+  if (tma_store) {
+    const uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batchA};
+    const uint64_t str[2] = {(uint64_t)N * 2, (uint64_t)M * (uint64_t)N * 2};
+    const uint32_t box[3] = {64, 32, 1};
+    if (encode_map(&tmC, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, C, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  }
+
   qg::W8A8Params p;
+  p.tma_store = tma_store ? 1 : 0;
   p.scale_b = scale_b;
   p.scale_a = scale_a;
   p.C = C;
@@ -343,11 +355,11 @@ static int w8a8_impl(const int8_t* A, const int8_t* B, const float* scale_b, con
     return bf ? launch_w8_pair<false, true>(tmA, tmB, p, pgrid, s) : launch_w8_pair<false, false>(tmA, tmB, p, pgrid, s);
   }
   if (BN == 256) {
-    if (nk) return bf ? launch_w8<256, true, true>(tmA, tmB, p, grid, s) : launch_w8<256, true, false>(tmA, tmB, p, grid, s);
-    return bf ? launch_w8<256, false, true>(tmA, tmB, p, grid, s) : launch_w8<256, false, false>(tmA, tmB, p, grid, s);
+    if (nk) return bf ? launch_w8<256, true, true>(tmA, tmB, tmC, p, grid, s) : launch_w8<256, true, false>(tmA, tmB, tmC, p, grid, s);
+    return bf ? launch_w8<256, false, true>(tmA, tmB, tmC, p, grid, s) : launch_w8<256, false, false>(tmA, tmB, tmC, p, grid, s);
   }
-  if (nk) return bf ? launch_w8<128, true, true>(tmA, tmB, p, grid, s) : launch_w8<128, true, false>(tmA, tmB, p, grid, s);
-  return bf ? launch_w8<128, false, true>(tmA, tmB, p, grid, s) : launch_w8<128, false, false>(tmA, tmB, p, grid, s);
+  if (nk) return bf ? launch_w8<128, true, true>(tmA, tmB, tmC, p, grid, s) : launch_w8<128, true, false>(tmA, tmB, tmC, p, grid, s);
+  return bf ? launch_w8<128, false, true>(tmA, tmB, tmC, p, grid, s) : launch_w8<128, false, false>(tmA, tmB, tmC, p, grid, s);
 }
 
 int qgemm_w8a8(const int8_t* A, const int8_t* B, const float* scale_b, const float* scale_a, void* C,

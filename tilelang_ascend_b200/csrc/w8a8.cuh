@@ -29,6 +29,7 @@ struct W8A8Params {
   // of the table is (group, first row, valid rows <= 128).  Null for the plain and batched forms.
   const int* meta;
   int groups;
+  int tma_store;  // C is written with tiled bulk stores from a shared-memory staging tile (needs bn % 64 == 0)
 };
 
 // One output tile's coordinates: batch index of B / scale_b, batch index of A / C / scale_a, first row, valid rows.
@@ -51,7 +52,8 @@ struct W8Cfg {
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int BAR_BYTES = 256;
   static constexpr int SCALE_BYTES = 4 * BN * 4;  // each epilogue warp's copy of the tile's column scales
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + SCALE_BYTES + 1024;  // + alignment slack
+  static constexpr int OUT_BYTES = 4 * 4096;      // each epilogue warp's staging tile: 32 rows x 64 outputs
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + BAR_BYTES + SCALE_BYTES + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ void w8_decode_tile(const W8A8Params& p, int tile, int& b, int& m_blk, int& n_blk) {
@@ -91,13 +93,14 @@ __device__ __forceinline__ W8Tile w8_tile(const W8A8Params& p, int tile) {
 template <int BN, bool B_NK, bool OUT_BF16>
 __global__ void __launch_bounds__(W8_THREADS, 1)
 w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const W8A8Params p) {
+                 const __grid_constant__ CUtensorMap tmC, const W8A8Params p) {
   using Cfg = W8Cfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint8_t* out_stage = smem + STAGES * Cfg::STAGE_BYTES;  // 1024-byte aligned: 128-byte swizzled staging tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + Cfg::OUT_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + STAGES;
   uint64_t* tfull = bars + 2 * STAGES;
@@ -118,6 +121,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&tfull[i], 1);
       mbar_init(&tempty[i], 4);
     }
+    if (p.tma_store) tma_prefetch_desc(&tmC);
     mbar_init(drain, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -226,7 +230,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // accumulators (the loads hide behind the main loop), and keeps the next 32-column chunk's tcgen05.ld in
     // flight while it converts and stores the current one.
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
-    float* sb_s = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::BAR_BYTES) + q * BN;
+    float* sb_s = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + Cfg::BAR_BYTES) + q * BN;
+    uint8_t* my_stage = out_stage + q * 4096;  // [32 rows][128 B], 16-byte piece j of row r at (j ^ (r & 7))
     int it = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const W8Tile t = w8_tile(p, tile);
@@ -251,10 +256,17 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const size_t row_off = ((size_t)t.bA * p.M + (row_ok ? m : 0)) * (size_t)p.N;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
       const int chunks = p.bn >> 5;
+      // Whole row blocks go out as tiled bulk stores (coalesced, clipped at the tensor's edge); a partial
+      // block of the grouped form must not touch the rows after it and uses per-row stores.
+      const bool tma_out = p.tma_store != 0 && (p.meta == nullptr || t.rows == W8_BM);
       uint32_t r[2][32];
       tmem_ld_32x32b_x32(taddr, r[0]);
 #pragma unroll 1
       for (int c2 = 0; c2 < chunks; c2 += 2) {
+        if (tma_out) {  // the previous bulk store has read the staging tile
+          if (lane == 0) bulk_wait_group_read0();
+          __syncwarp();
+        }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int c = c2 + h;
@@ -262,14 +274,36 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_wait();                                                     // chunk c is in r[h]
           if (c + 1 < chunks) tmem_ld_32x32b_x32(taddr + (c + 1) * 32, r[h ^ 1]);  // chunk c + 1 in flight
           const int n = n_blk * p.bn + c * 32;
-          if (row_ok && n < p.N) {
-            if (p.acc_out != nullptr) {
-              int4* dst = reinterpret_cast<int4*>(p.acc_out + row_off + n);
+          if (row_ok && n < p.N && p.acc_out != nullptr) {
+            int4* dst = reinterpret_cast<int4*>(p.acc_out + row_off + n);
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (n + 4 * j < p.N)
-                  dst[j] = make_int4((int)r[h][4 * j], (int)r[h][4 * j + 1], (int)r[h][4 * j + 2], (int)r[h][4 * j + 3]);
+            for (int j = 0; j < 8; ++j)
+              if (n + 4 * j < p.N)
+                dst[j] = make_int4((int)r[h][4 * j], (int)r[h][4 * j + 1], (int)r[h][4 * j + 2], (int)r[h][4 * j + 3]);
+          }
+          if (tma_out) {
+            if (n < p.N) {
+              const float4* sv = reinterpret_cast<const float4*>(sb_s + c * 32);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float4 s_lo = sv[2 * j], s_hi = sv[2 * j + 1];
+                const float sc[8] = {s_lo.x, s_lo.y, s_lo.z, s_lo.w, s_hi.x, s_hi.y, s_hi.z, s_hi.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int col = 8 * j + 2 * e;
+                  float f0 = __int2float_rn((int)r[h][col]);
+                  float f1 = __int2float_rn((int)r[h][col + 1]);
+                  if (p.sa_mode != 0) { f0 = __fmul_rn(f0, sa); f1 = __fmul_rn(f1, sa); }
+                  f0 = __fmul_rn(f0, sc[2 * e]);
+                  f1 = __fmul_rn(f1, sc[2 * e + 1]);
+                  o[e] = pack_out2<OUT_BF16>(f0, f1);
+                }
+                *reinterpret_cast<uint4*>(my_stage + lane * 128 + (((h * 4 + j) ^ (lane & 7)) << 4)) =
+                    make_uint4(o[0], o[1], o[2], o[3]);
+              }
             }
+          } else if (row_ok && n < p.N) {
             if (p.C != nullptr) {
               uint16_t* cbase = reinterpret_cast<uint16_t*>(p.C) + row_off + n;
               const float4* sv = reinterpret_cast<const float4*>(sb_s + c * 32);
@@ -295,11 +329,20 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         }
+        if (tma_out && n_blk * p.bn + c2 * 32 < p.N && t.m0 + q * 32 < p.M) {  // a box wholly outside is not issued
+          fence_proxy_async_smem();  // this thread's staging writes are visible to the bulk-copy engine
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tmC, my_stage, n_blk * p.bn + c2 * 32, t.m0 + q * 32, t.bA);
+            bulk_commit_group();
+          }
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[buf]);
     }
+    if (lane == 0) bulk_wait_group_read0();  // the staging tile must outlive the last bulk store's read
   }
 
   // ------------------------------------------------------------------ teardown
