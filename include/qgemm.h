@@ -104,7 +104,7 @@ int qgemm_w8a8_grouped(const int8_t* A, const int8_t* B, const float* scale_b, c
                        int b_layout, uint32_t* status, void* stream);
 
 /* Bytes of scratch memory qgemm_w4a16 needs for this problem on the current device (split-K partial
- * sums and arrival counters).  The first use of a scratch buffer must find its first
+ * sums and arrival counters, the prepared activations and, from 1024 tokens on, the weights as f16: 2*N*K).  The first use of a scratch buffer must find its first
  * qgemm_w4a16_counter_bytes() bytes zeroed; the kernel leaves them zero.  Two launches that may
  * overlap on the device must not share a scratch buffer. */
 int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K);

@@ -232,3 +232,55 @@ def test_rejects_bad_arguments():
     with pytest.raises(q.QGemmError, match="group"):
         q.w4a16_gemm(A, P, torch.ones(4, 16, dtype=torch.float16, device="cuda"), 8, 16)
     assert torch.equal(q.w4a16_gemm(A, P).cpu(), torch.zeros(4, 16, dtype=torch.float16))
+
+
+def test_dequantise_once_path_small_shapes():
+    """Above QGEMM_W4_GEMM_MIN_M tokens (default 1024) the weights are dequantised to f16 once and multiplied by
+    the f16 tensor-core GEMM.  The threshold is read once per process, so a child process with a low threshold
+    runs that path on small ragged shapes: scaled / unscaled, every group size, f16 / bf16, batched."""
+    import os
+    import subprocess
+    import sys
+    code = r"""
+import torch
+from oracle import qgemm_oracle as oc
+import tilelang_ascend_b200 as q
+def close(C, ref): torch.testing.assert_close(C.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
+for M, K, N, dt, group in [(17, 256, 128, "float16", 128), (40, 512, 272, "bfloat16", 64), (200, 1024, 528, "float16", 32),
+                           (130, 768, 2320, "bfloat16", 256), (300, 512, 144, "float16", 512), (129, 2048, 1024, "bfloat16", 128)]:
+    A, P, S = oc.make_w4a16_inputs(M, K, N, dt, group, seed=M + K)
+    C = q.w4a16_gemm(A.cuda(), P.cuda(), S.cuda(), 8, group)
+    close(C, oc.dequant_gemm_fp16_ref(A, P, dt, S, 8, group))
+    C0 = q.w4a16_gemm(A.cuda(), P.cuda(), None)
+    close(C0, oc.dequant_gemm_fp16_ref(A, P, dt))
+# exact dequantisation: unit activations read back half(q - zero) * s bit for bit
+K, N, group = 256, 144, 64
+_, P, S = oc.make_w4a16_inputs(1, K, N, "float16", group, seed=3)
+eye = torch.eye(K, dtype=torch.float16)
+W = q.w4a16_gemm(eye.cuda(), P.cuda(), S.cuda(), 8, group)   # [K, N] = dequantised weights, transposed
+assert torch.equal(W.cpu().t().contiguous(), oc.dequant_weight_ref(P, S, 8, group).half())
+# batched
+ins = [oc.make_w4a16_inputs(48, 512, 272, "float16", 128, seed=s) for s in range(3)]
+A, P, S = [torch.stack([x[i] for x in ins]).cuda() for i in range(3)]
+C = q.w4a16_gemm(A, P, S, 8, 128)
+for b in range(3): close(C[b], oc.dequant_gemm_fp16_ref(ins[b][0], ins[b][1], "float16", ins[b][2], 8, 128))
+print("dequantise-once ok")
+"""
+    env = dict(os.environ, QGEMM_W4_GEMM_MIN_M="17")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "dequantise-once ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_config5_prefill_m4096_band_and_linearity():
+    """Config 5 at 4096 tokens goes through the dequantise-once path at full size: bands of output columns
+    against the oracle, and f(2A) == 2 f(A) over the whole output."""
+    q = _q()
+    A, packed, scales = oc.make_config_inputs("cfg5", M=4096)
+    Ad, Pd, Sd = A.cuda(), packed.cuda(), scales.cuda()
+    C = q.w4a16_gemm(Ad, Pd, Sd, 8, 128)
+    cols = torch.cat([torch.arange(0, 64), torch.arange(20000, 20064), torch.arange(28672 - 64, 28672)])
+    ref = oc.dequant_gemm_fp16_ref(A, packed[cols], "bfloat16", scales[:, cols].contiguous(), 8, 128)
+    _close(C[:, cols.cuda()], ref)
+    C2 = q.w4a16_gemm(Ad * 2, Pd, Sd, 8, 128)
+    torch.testing.assert_close(C2.float(), C.float() * 2, rtol=1e-2, atol=1e-2)

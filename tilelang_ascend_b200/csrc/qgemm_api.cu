@@ -58,6 +58,8 @@ int set_smem_w8() {
   if (set_smem(qg::w8a8_gemm_kernel<BN, false, true>, C::SMEM_BYTES)) return -1;
   if (set_smem(qg::w8a8_gemm_kernel<BN, true, false>, C::SMEM_BYTES)) return -1;
   if (set_smem(qg::w8a8_gemm_kernel<BN, true, true>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w8a8_gemm_kernel<BN, true, false, true>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w8a8_gemm_kernel<BN, true, true, true>, C::SMEM_BYTES)) return -1;
   return 0;
 }
 template <int FLUSH>
@@ -384,19 +386,90 @@ int qgemm_w8a8_grouped(const int8_t* A, const int8_t* B, const float* scale_b, c
 
 int64_t qgemm_w4a16_counter_bytes(void) { return kW4CounterBytes; }
 
+// Token counts from this on (and N a multiple of 16) dequantise the whole weight matrix to f16 once and run
+// the f16 tensor-core GEMM on it: above a few hundred tokens the in-flight conversion, repeated for every
+// 128-token tile, costs more than writing and re-reading 2 bytes per weight.  QGEMM_W4_GEMM_MIN_M overrides
+// the threshold (0 = never).
+int64_t w4_gemm_min_m() {
+  static int64_t v = -1;
+  if (v < 0) {
+    v = 1024;
+    if (const char* e = getenv("QGEMM_W4_GEMM_MIN_M")) v = atoll(e) > 0 ? atoll(e) : (1ll << 62);
+    if (v <= 16) v = 17;  // the small-token kernels keep their range
+  }
+  return v;
+}
+bool w4_use_f16_gemm(int64_t M, int64_t N) { return M >= w4_gemm_min_m() && (N % 16) == 0; }
+
 int64_t qgemm_w4a16_batched_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K) {
-  (void)N;
   int sms = 0;
   if (ensure_device(&sms)) return -1;
   const int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
   const int mt = w4_pick_mt(M);
   // the arrival counters first (fixed place whatever the tile height), then two partial slots of
   // [MT][128] fp32 per CTA, then the f16 copy of the activations in the kernel's K order
-  return kW4CounterBytes + grid * 2 * (int64_t)mt * 128 * 4 + batch * M * K * 2;
+  // ... and, for the large-token path, the dequantised f16 weights
+  return kW4CounterBytes + grid * 2 * (int64_t)mt * 128 * 4 + batch * M * K * 2 +
+         (w4_use_f16_gemm(M, N) ? batch * N * K * 2 : 0);
 }
 
 int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   return qgemm_w4a16_batched_workspace_bytes(1, M, N, K);
+}
+
+// C[b] = A16[b] (f16 [M, K]) x W16[b]^T (f16 [N, K]), fp32 accumulation, f16 / bf16 out: the tile pipeline of
+// the W8A8 kernel on 2-byte elements (K counted in bytes).
+static int w4_f16_gemm(const void* A16, const void* W16, void* C, int64_t batch, int64_t M, int64_t N, int64_t K,
+                       bool bf, uint32_t* status, cudaStream_t s, int sms) {
+  const int64_t Kb = K * 2;
+  CUtensorMap tmA, tmB, tmC;
+  {
+    const uint64_t dims[3] = {(uint64_t)Kb, (uint64_t)M, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)Kb, (uint64_t)M * (uint64_t)Kb};
+    const uint32_t box[3] = {128, 128, 1};
+    if (encode_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, A16, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  }
+  const int64_t m_tiles = (M + 127) / 128;
+  const int BN = (N > 128 && batch * m_tiles * ((N + 255) / 256) >= sms) ? 256 : 128;
+  {
+    const uint64_t dims[3] = {(uint64_t)Kb, (uint64_t)N, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)Kb, (uint64_t)N * (uint64_t)Kb};
+    const uint32_t box[3] = {128, (uint32_t)BN, 1};
+    if (encode_map(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, W16, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
+    const uint64_t str[2] = {(uint64_t)N * 2, (uint64_t)M * (uint64_t)N * 2};
+    const uint32_t box[3] = {64, 32, 1};
+    if (encode_map(&tmC, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, C, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  }
+  qg::W8A8Params p;
+  memset(&p, 0, sizeof(p));
+  p.C = C;
+  p.batch = (int)batch;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)Kb;
+  p.m_tiles = (int)m_tiles;
+  p.n_tiles = (int)((N + BN - 1) / BN);
+  p.bn = BN;
+  const int64_t num_tiles = batch * p.m_tiles * p.n_tiles;
+  if (num_tiles > 0x7fffffff) return fail("qgemm_w4a16: too many tiles");
+  p.num_tiles = (int)num_tiles;
+  p.k_blocks = (int)((Kb + 127) / 128);
+  p.status = status;
+  p.wait_limit_ns = g_wait_limit_ns;
+  p.tma_store = 1;
+  const int grid = (int)(num_tiles < sms ? num_tiles : sms);
+  if (BN == 256) {
+    if (bf) qg::w8a8_gemm_kernel<256, true, true, true><<<grid, qg::W8_THREADS, qg::W8Cfg<256>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+    else qg::w8a8_gemm_kernel<256, true, false, true><<<grid, qg::W8_THREADS, qg::W8Cfg<256>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+  } else {
+    if (bf) qg::w8a8_gemm_kernel<128, true, true, true><<<grid, qg::W8_THREADS, qg::W8Cfg<128>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+    else qg::w8a8_gemm_kernel<128, true, false, true><<<grid, qg::W8_THREADS, qg::W8Cfg<128>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+  }
+  CUDA_OK(cudaGetLastError());
+  return 0;
 }
 
 int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
@@ -493,6 +566,19 @@ int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scal
                                                                   reinterpret_cast<uint4*>(a_prepared), n_chunks,
                                                                   a_dtype == QGEMM_DT_BF16 ? 1 : 0);
     CUDA_OK(cudaGetLastError());
+  }
+  if (w4_use_f16_gemm(M, N)) {
+    uint8_t* w16 = a_prepared + batch * M * K * 2;
+    const int64_t geff = group > K ? K : group;
+    const long long n_chunks = (long long)batch * N * (K / 32);
+    const long long blocks = (n_chunks + 255) / 256;
+    if (blocks > 0x7fffffffll) return fail("qgemm_w4a16: weight tensor too large");
+    qg::w4a16_dequant_weights<<<(unsigned)blocks, 256, 0, s>>>(reinterpret_cast<const uint4*>(B_packed),
+                                                             static_cast<const __half*>(scales),
+                                                             reinterpret_cast<uint4*>(w16), n_chunks, (int)(K / 32),
+                                                             (int)N, (int)K, (int)geff, zero);
+    CUDA_OK(cudaGetLastError());
+    return w4_f16_gemm(a_prepared, w16, C, batch, M, N, K, bf, status, s, sms);
   }
   if (w4_use_decode(M)) {
     if (scales == nullptr) return launch_w4d<0>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);

@@ -148,6 +148,39 @@ __device__ __forceinline__ uint4 w4_permute_act(uint4 v) {
   return o;
 }
 
+// Whole-matrix dequantisation for the large-token path: packed [rows, K/2] + scales [K/group, N] per problem
+// -> f16 [rows, K] with every group of eight K values in the order 0,4,1,5,2,6,3,7 (what w4_dequant8 emits and
+// what w4a16_prepare_activations gives the activations), same values as the GEMM kernels' in-flight
+// conversion.  One 16-byte packed chunk (32 weights -> 64 bytes) per thread, consecutive threads along K.
+__global__ void __launch_bounds__(256)
+w4a16_dequant_weights(const uint4* __restrict__ packed, const __half* __restrict__ scales, uint4* __restrict__ out,
+                      long long n_chunks, int chunks_per_row, int N, int K, int group, int zero) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_chunks) return;
+  const long long row = i / chunks_per_row;  // batch * N + n
+  const int k0 = (int)(i - row * chunks_per_row) * 32;
+  const uint4 v = __ldcs(packed + i);
+  const uint32_t z = (uint32_t)zero;
+  const uint32_t sub_lo = (0x6400u + z) * 0x00010001u;
+  const uint32_t sub_hi = ((0x5400u + (z << 4)) | 0x8000u) * 0x00010001u;
+  uint32_t s2 = 0x3C003C00u;
+  const bool scaled = scales != nullptr;
+  if (scaled) {
+    const long long b = row / N;
+    const int n = (int)(row - b * N);
+    const int g = k0 / group;  // a 32-wide chunk never straddles a group (group is a multiple of 32)
+    s2 = (uint32_t)__half_as_ushort(scales[(b * (K / group) + g) * (long long)N + n]) * 0x00010001u;
+  }
+  uint32_t o[16];
+  w4_dequant8(v.x, sub_lo, sub_hi, s2, scaled, o + 0);
+  w4_dequant8(v.y, sub_lo, sub_hi, s2, scaled, o + 4);
+  w4_dequant8(v.z, sub_lo, sub_hi, s2, scaled, o + 8);
+  w4_dequant8(v.w, sub_lo, sub_hi, s2, scaled, o + 12);
+  uint4* dst = out + i * 4;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) __stcs(dst + j, make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
+}
+
 // Pre-pass: activations [M, K] (f16 or bf16) -> f16 with every group of eight K values reordered to
 // 0,4,1,5,2,6,3,7.  One 16-byte chunk per thread.
 __global__ void __launch_bounds__(256)

@@ -90,7 +90,10 @@ __device__ __forceinline__ W8Tile w8_tile(const W8A8Params& p, int tile) {
   return t;
 }
 
-template <int BN, bool B_NK, bool OUT_BF16>
+// F16 = true runs the same pipeline on f16 operands (kind::f16, fp32 accumulators, no scales): one MMA K step
+// is 32 bytes for both element types, so with K counted in bytes (p.K, p.k_blocks) nothing else changes.  It
+// serves the large-token W4A16 path, whose weights are dequantised to f16 once and then multiplied here.
+template <int BN, bool B_NK, bool OUT_BF16, bool F16 = false>
 __global__ void __launch_bounds__(W8_THREADS, 1)
 w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const W8A8Params p) {
@@ -182,7 +185,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, B_NK ? 0 : 1, W8_BM, (uint32_t)p.bn);
+      const uint32_t idesc = F16 ? make_idesc(ACC_F32, FMT_F16, FMT_F16, 0, B_NK ? 0 : 1, W8_BM, (uint32_t)p.bn)
+                                 : make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, B_NK ? 0 : 1, W8_BM, (uint32_t)p.bn);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -209,7 +213,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               // [K rows][128 B of N]: 32 K rows per MMA = 4096 B; the next 128 columns are one box (16 KB) further.
               bdesc = make_desc_mnmajor(sB + k * (W8_UMMA_K * 128), W8_BK * 128);
             }
-            umma_i8_ss(d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (F16) umma_f16_ss(d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_i8_ss(d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -242,7 +247,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool row_ok = q * 32 + lane < t.rows;
       float sa = 1.0f;
       if (p.sa_mode != 0 && row_ok) sa = __ldg(p.scale_a + (p.sa_mode == 2 ? (size_t)t.bA * p.M : 0) + m);
-      if (p.C != nullptr) {
+      if (!F16 && p.C != nullptr) {
         const float* sbp = p.scale_b + (p.sb_mode == 2 ? (size_t)t.bB * p.N : 0);
         __syncwarp();  // the previous tile's reads of sb_s are done
         for (int c = lane; c < p.bn; c += 32) {
@@ -292,11 +297,17 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const int col = 8 * j + 2 * e;
-                  float f0 = __int2float_rn((int)r[h][col]);
-                  float f1 = __int2float_rn((int)r[h][col + 1]);
-                  if (p.sa_mode != 0) { f0 = __fmul_rn(f0, sa); f1 = __fmul_rn(f1, sa); }
-                  f0 = __fmul_rn(f0, sc[2 * e]);
-                  f1 = __fmul_rn(f1, sc[2 * e + 1]);
+                  float f0, f1;
+                  if constexpr (F16) {
+                    f0 = __uint_as_float(r[h][col]);
+                    f1 = __uint_as_float(r[h][col + 1]);
+                  } else {
+                    f0 = __int2float_rn((int)r[h][col]);
+                    f1 = __int2float_rn((int)r[h][col + 1]);
+                    if (p.sa_mode != 0) { f0 = __fmul_rn(f0, sa); f1 = __fmul_rn(f1, sa); }
+                    f0 = __fmul_rn(f0, sc[2 * e]);
+                    f1 = __fmul_rn(f1, sc[2 * e + 1]);
+                  }
                   o[e] = pack_out2<OUT_BF16>(f0, f1);
                 }
                 *reinterpret_cast<uint4*>(my_stage + lane * 128 + (((h * 4 + j) ^ (lane & 7)) << 4)) =
@@ -316,11 +327,17 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
                     const int col = 8 * j + 2 * e;
-                    float f0 = __int2float_rn((int)r[h][col]);
-                    float f1 = __int2float_rn((int)r[h][col + 1]);
-                    if (p.sa_mode != 0) { f0 = __fmul_rn(f0, sa); f1 = __fmul_rn(f1, sa); }
-                    f0 = __fmul_rn(f0, sc[2 * e]);
-                    f1 = __fmul_rn(f1, sc[2 * e + 1]);
+                    float f0, f1;
+                    if constexpr (F16) {
+                      f0 = __uint_as_float(r[h][col]);
+                      f1 = __uint_as_float(r[h][col + 1]);
+                    } else {
+                      f0 = __int2float_rn((int)r[h][col]);
+                      f1 = __int2float_rn((int)r[h][col + 1]);
+                      if (p.sa_mode != 0) { f0 = __fmul_rn(f0, sa); f1 = __fmul_rn(f1, sa); }
+                      f0 = __fmul_rn(f0, sc[2 * e]);
+                      f1 = __fmul_rn(f1, sc[2 * e + 1]);
+                    }
                     o[e] = pack_out2<OUT_BF16>(f0, f1);
                   }
                   *reinterpret_cast<uint4*>(cbase + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
