@@ -48,12 +48,29 @@ __device__ __forceinline__ void aq_unpack8(const uint4& v, bool bf16, float (&f)
   }
 }
 
-__device__ __forceinline__ float aq_absmax8(const uint4& v, bool bf16, float m) {
-  float f[8];
-  aq_unpack8(v, bf16, f);
+// Running abs-max of a row piece, kept as a packed pair in the input's own 16-bit format (the maximum of
+// absolute values is exact in any format): one abs + one max per two elements.
+__device__ __forceinline__ uint32_t aq_absmax8(const uint4& v, bool bf16, uint32_t m2) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(f[i]));
-  return m;
+  for (int i = 0; i < 4; ++i) {
+    if (bf16) {
+      const __nv_bfloat162 a = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      const __nv_bfloat162 r = __hmax2(a, *reinterpret_cast<const __nv_bfloat162*>(&m2));
+      m2 = *reinterpret_cast<const uint32_t*>(&r);
+    } else {
+      const __half2 a = __habs2(*reinterpret_cast<const __half2*>(&w[i]));
+      const __half2 r = __hmax2(a, *reinterpret_cast<const __half2*>(&m2));
+      m2 = *reinterpret_cast<const uint32_t*>(&r);
+    }
+  }
+  return m2;
+}
+
+__device__ __forceinline__ float aq_pair_max(uint32_t m2, bool bf16) {
+  if (bf16) return fmaxf(__uint_as_float(m2 << 16), __uint_as_float(m2 & 0xffff0000u));
+  const __half2 h = *reinterpret_cast<const __half2*>(&m2);
+  return fmaxf(__low2float(h), __high2float(h));
 }
 
 // x / scale rounded to the nearest integer (ties to even), eight values packed into two words.
@@ -110,18 +127,19 @@ __global__ void __launch_bounds__(AQ_THREADS) act_quant_kernel(const ActQuantPar
   const uint4* x = p.X + (live ? row : 0) * chunks;
 
   uint4 keep[KEEP];
-  float m = 0.f;
+  uint32_t m2 = 0u;  // (+0, +0) in either format
   if (live) {
 #pragma unroll
     for (int i = 0; i < KEEP; ++i) {
       const int c = t + i * TPR;
       if (c < chunks) {
         keep[i] = __ldcs(x + c);
-        m = aq_absmax8(keep[i], bf16, m);
+        m2 = aq_absmax8(keep[i], bf16, m2);
       }
     }
-    for (int c = t + KEEP * TPR; c < chunks; c += TPR) m = aq_absmax8(__ldg(x + c), bf16, m);
+    for (int c = t + KEEP * TPR; c < chunks; c += TPR) m2 = aq_absmax8(__ldg(x + c), bf16, m2);
   }
+  float m = aq_pair_max(m2, bf16);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if (WPR > 1) {
