@@ -11,7 +11,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from oracle import qgemm_oracle as oc
-from tilelang_ascend_b200.dist import ColumnShardedW4A16, shard_batches, shard_range
+from tilelang_ascend_b200.dist import ColumnShardedW4A16, GroupShardedW8A8, shard_batches, shard_groups, shard_range
 
 
 def _free_port():
@@ -83,6 +83,35 @@ def _worker_peer_leaves(rank, world, port, q):
         q.put((rank, False, repr(exc)))
 
 
+def _cpu_grouped(A, B, meta, scale, scale_a=None, out_dtype=torch.bfloat16):
+    return oc.grouped_quant_matmul_ref(A, B, meta, scale, out_dtype, scale_a=scale_a)
+
+
+def _cpu_meta(sizes, block_M, device=None):
+    return oc.build_block_metadata_ref(sizes, block_M)
+
+
+def _worker_group_shard(rank, world, port, q):
+    try:
+        _init(rank, world, port)
+        sizes, K, N = [63, 0, 140, 77, 5], 64, 48
+        g = torch.Generator().manual_seed(8)  # same seed on every rank
+        A = torch.randint(-128, 128, (sum(sizes), K), dtype=torch.int8, generator=g)
+        B = torch.randint(-128, 128, (len(sizes), K, N), dtype=torch.int8, generator=g)
+        sb = torch.rand((len(sizes), N), generator=g) * 0.02 + 0.001
+        sa = torch.rand(sum(sizes), generator=g) * 0.02 + 0.001
+        layer = GroupShardedW8A8(sizes, B, sb, out_dtype=torch.bfloat16, gemm=_cpu_grouped, metadata=_cpu_meta)
+        r0, r1 = layer.row0, layer.row1
+        full = layer(A[r0:r1], sa[r0:r1], gather=True)
+        ref = oc.grouped_quant_matmul_ref(A, B, oc.build_block_metadata_ref(sizes, 128), sb, torch.bfloat16, scale_a=sa)
+        local = layer(A[r0:r1], sa[r0:r1])
+        ok = torch.equal(full, ref) and torch.equal(local, ref[r0:r1]) and layer.B_local.shape[0] == layer.g1 - layer.g0
+        q.put((rank, bool(ok), ""))
+        dist.destroy_process_group()
+    except Exception as exc:  # pragma: no cover
+        q.put((rank, False, repr(exc)))
+
+
 def _run(worker, world=2, timeout=120):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -129,4 +158,20 @@ def test_batch_sharded_w8a8_two_ranks():
 
 def test_peer_leaving_between_steps_gives_an_error():
     res = _run(_worker_peer_leaves)
+    assert all(ok for _, ok, _ in res), res
+
+
+def test_shard_groups_covers_all_rows():
+    sizes = [63, 0, 140, 77, 5, 300, 12]
+    for world in (1, 2, 3, 8):
+        spans = [shard_groups(sizes, world, r) for r in range(world)]
+        assert spans[0][0] == 0 and spans[0][2] == 0 and spans[-1][1] == len(sizes) and spans[-1][3] == sum(sizes)
+        for a, b in zip(spans, spans[1:]):
+            assert a[1] == b[0] and a[3] == b[2]
+        for g0, g1, r0, r1 in spans:
+            assert r1 - r0 == sum(sizes[g0:g1])
+
+
+def test_group_sharded_w8a8_two_ranks():
+    res = _run(_worker_group_shard)
     assert all(ok for _, ok, _ in res), res

@@ -7,6 +7,9 @@
   ``scales[K/g, N]``) shard across ranks, activations are replicated, and the ``[M, N/g]`` output blocks
   are reassembled with one all-gather (NCCL over NVLink on GPUs, gloo in the CPU tests).
 
+* Grouped (ragged) W8A8: whole groups (experts) shard across ranks; each rank holds its experts' weights and
+  scales and receives only its groups' rows, so again no collective on the data path.
+
 No kernel reads another GPU's memory: operands are resident on their rank, only outputs move.
 The reference has no counterpart (its only multi-device code is one-sided SHMEM demos).
 """
@@ -74,5 +77,69 @@ class ColumnShardedW4A16:
         parts = torch.empty((self.world * M, nl), dtype=C_local.dtype, device=C_local.device)
         dist.all_gather_into_tensor(parts, C_local, group=self.pg)  # rank r's block lands in rows [r*M, (r+1)*M)
         return parts.view(self.world, M, nl).permute(1, 0, 2).reshape(M, self.world * nl)
+
+    __call__ = forward
+
+
+def shard_groups(batch_sizes_list, world: int, rank: int):
+    """Expert-parallel split of a grouped (ragged) problem: contiguous groups per rank.
+
+    Returns ``(g0, g1, row0, row1)``: this rank owns groups [g0, g1) and therefore rows [row0, row1) of the
+    stacked ``A`` / ``C``.  Groups are dealt as ``shard_range`` deals batches; sizes may differ, so the row counts
+    per rank differ too (ragged groups are balanced by the caller's routing, not here)."""
+    sizes = [int(x) for x in batch_sizes_list]
+    g0, g1 = shard_range(len(sizes), world, rank)
+    row0 = sum(sizes[:g0])
+    return g0, g1, row0, row0 + sum(sizes[g0:g1])
+
+
+class GroupShardedW8A8:
+    """Grouped W8A8 layer whose groups (experts) are split over the ranks of a process group.
+
+    Holds this rank's ``B[g0:g1]`` and ``scale[g0:g1]``.  ``forward(A_local, scale_a_local)`` takes this rank's rows
+    of the stacked activations (rows ``row0:row1`` of the global stack) and returns the matching rows of the
+    output; ``gather=True`` all-gathers the (ragged) row blocks into the full ``[total_M, N]`` on every rank."""
+
+    def __init__(self, batch_sizes_list, B: torch.Tensor, scale: torch.Tensor, out_dtype=torch.bfloat16,
+                 group: Optional[dist.ProcessGroup] = None, gemm: Optional[Callable] = None,
+                 metadata: Optional[Callable] = None):
+        self.pg = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.sizes = [int(x) for x in batch_sizes_list]
+        self.g0, self.g1, self.row0, self.row1 = shard_groups(self.sizes, self.world, self.rank)
+        self.B_local = B[self.g0:self.g1].contiguous()
+        self.scale_local = scale[self.g0:self.g1].contiguous() if scale.dim() == 2 else scale
+        self.out_dtype = out_dtype
+        if gemm is None:
+            from .ops import grouped_quant_matmul as gemm
+        if metadata is None:
+            from .ops import build_block_metadata as metadata
+        self._gemm, self._meta_fn, self._meta = gemm, metadata, None
+
+    def to(self, device):
+        self.B_local = self.B_local.to(device)
+        self.scale_local = self.scale_local.to(device)
+        self._meta = None
+        return self
+
+    def forward(self, A_local: torch.Tensor, scale_a_local: Optional[torch.Tensor] = None, gather: bool = False):
+        if A_local.shape[0] != self.row1 - self.row0:
+            raise ValueError(f"rank {self.rank} owns {self.row1 - self.row0} rows, got {A_local.shape[0]}")
+        if self._meta is None or self._meta.device != A_local.device:
+            self._meta = self._meta_fn(self.sizes[self.g0:self.g1], 128, A_local.device)
+        C_local = self._gemm(A_local, self.B_local, self._meta, self.scale_local, scale_a_local, out_dtype=self.out_dtype)
+        if not gather or self.world == 1:
+            return C_local
+        # ragged row blocks: pad each rank's block to the largest one, gather once, cut the padding off
+        counts = [r1 - r0 for _, _, r0, r1 in (shard_groups(self.sizes, self.world, r) for r in range(self.world))]
+        most, n = max(counts), C_local.shape[1]
+        padded = C_local
+        if C_local.shape[0] < most:
+            padded = torch.zeros((most, n), dtype=C_local.dtype, device=C_local.device)
+            padded[:C_local.shape[0]] = C_local
+        parts = torch.empty((self.world * most, n), dtype=C_local.dtype, device=C_local.device)
+        dist.all_gather_into_tensor(parts, padded, group=self.pg)
+        return torch.cat([parts[r * most:r * most + c] for r, c in enumerate(counts)], dim=0)
 
     __call__ = forward
