@@ -144,6 +144,35 @@ int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scal
                         int a_dtype, int out_dtype, uint32_t* status, void* stream);
 
 /*
+ * W4A16 with the other weight formats of tilelang/quantize: everything as qgemm_w4a16_batched, plus
+ *
+ * weight_format  QGEMM_W4_SEQUENTIAL: nibble j of a row at byte j/2, bits 4*(j%2) (general_compress,
+ *                tilelang/quantize/utils.py:53-69).  QGEMM_W4_INTERLEAVED_F16: every 32-bit word permuted by
+ *                interleave_weight(qweight, 4, "float16") (utils.py:73-99): elements 0,2,4,6 in the low
+ *                half-word, 1,3,5,7 in the high one, the layout the reference's lop3 decode expects.
+ * zeros          nullable fp16 [batch, K/group, N]: one zero point per (group, output feature) instead of the
+ *                scalar `zero` (which is then ignored).  Needs scales and N % 16 == 0.
+ * zero_mode      how zeros enter (tilelang/quantize/lop3.py:135-175, 232-270, 325-358):
+ *                QGEMM_ZERO_ORIGINAL   W = (q - z) * s      (the scalar-zero operators use this form)
+ *                QGEMM_ZERO_RESCALE    W = q * s - |z|      (one f16 FMA; needs the zeros tensor)
+ *                QGEMM_ZERO_QUANTIZED  W = (q - qz) * s     with integer qz given as fp16 values (unpack
+ *                                      packed qzeros on the host first)
+ * With a zeros tensor the weights are dequantised once into the scratch buffer (f16 [batch, N, K]) and
+ * multiplied by the f16 tensor-core GEMM at every token count, so the scratch size comes from
+ * qgemm_w4a16_ex_workspace_bytes(..., has_zeros_tensor = 1).  Without one, the same kernels as qgemm_w4a16 run.
+ */
+#define QGEMM_W4_SEQUENTIAL 0
+#define QGEMM_W4_INTERLEAVED_F16 1
+#define QGEMM_ZERO_ORIGINAL 0
+#define QGEMM_ZERO_RESCALE 1
+#define QGEMM_ZERO_QUANTIZED 2
+int64_t qgemm_w4a16_ex_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K, int has_zeros_tensor);
+int qgemm_w4a16_ex(const void* A, const uint8_t* B_packed, const void* scales, const void* zeros, int zero,
+                   int zero_mode, int weight_format, int64_t group, void* C, void* workspace, int64_t workspace_bytes,
+                   int64_t batch, int64_t M, int64_t N, int64_t K, int a_dtype, int out_dtype, uint32_t* status,
+                   void* stream);
+
+/*
  * W4A16 dequantize-GEMM that needs no memory from the caller beyond inputs and output.  (No counterpart
  * in the reference: there the wrapper allocates every workspace with torch before the call.)
  *

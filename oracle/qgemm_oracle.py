@@ -193,6 +193,39 @@ def dequant_weight_ref(packed, scales=None, zero=8, group_size=128):
     return (q.to(torch.int16) - int(zero)).to(torch.float16) * s_full
 
 
+def dequant_weight_zeros_ref(packed, scales, zeros, group_size=128, zeros_mode="original"):
+    """Dequantised W[N, K] fp16 with one zero point per (group, output feature): ``zeros`` fp16 [K/g, N].
+
+    The three zero modes of tilelang/quantize/lop3.py (selected at :1097,1172-1180), each with the roundings of
+    the f16x2 instructions its decode routine issues:
+      "original"   (:135-168)  h = q - z (sub.f16x2), then h * s (fma with +0): two roundings
+      "rescale"    (:232-262)  fma(q, s, -|z|): one rounding (the routine ORs the sign bit into z, :247)
+      "quantized"  (:325-358)  (q - qz) * s with integer qz: the subtraction is exact, one rounding
+    ``q`` is the raw nibble value 0..15 (exact in f16)."""
+    q = unpack_uint4(packed).to(torch.float16)
+    N, K = q.shape
+    assert scales.shape == (K // group_size, N) and zeros.shape == (K // group_size, N)
+    s_full = scales.t().repeat_interleave(group_size, dim=1)
+    z_full = zeros.to(torch.float16).t().repeat_interleave(group_size, dim=1)
+    if zeros_mode in ("original", "quantized"):
+        return (q - z_full) * s_full
+    if zeros_mode == "rescale":
+        # q * s is exact in fp64 (4 x 11 significant bits) and so is the difference: one rounding to f16
+        return (q.double() * s_full.double() - z_full.double().abs()).to(torch.float16)
+    raise ValueError(zeros_mode)
+
+
+def interleave_int4_f16_ref(packed):
+    """interleave_weight(qweight, 4, "float16") of tilelang/quantize/utils.py:73-99, restated per 32-bit word:
+    element o (bits 4o) moves to bits (o % 2) * 16 + (o // 2) * 4."""
+    w = packed.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    out = torch.zeros_like(w)
+    for o in range(8):
+        out |= ((w >> (4 * o)) & 0xF) << ((o % 2) * 16 + (o // 2) * 4)
+    out = torch.where(out >= 2 ** 31, out - 2 ** 32, out).to(torch.int32)
+    return out.view(torch.uint8).reshape(packed.shape)
+
+
 def dequant_gemm_fp16_ref(A, packed, output_dtype, scales=None, zero=8, group_size=128):
     """``C = fp32(A) @ fp32(W).T`` cast to ``output_dtype``.
 

@@ -152,6 +152,14 @@ def main():
     out["grouped_gemm"] = dict(sizes=np.array(sizes, dtype=np.int64), block_M=np.array([bm], dtype=np.int64),
                                A=to_np(A), B=to_np(B), meta=to_np(meta), acc=to_np(acc))
 
+    # --- interleave_weight (tilelang/quantize/utils.py:73-126): the combinations that run in the reference ----
+    torch.manual_seed(3)
+    qw = torch.randint(-128, 128, (6, 32), dtype=torch.int8)
+    out["interleave_weight"] = dict(qweight=to_np(qw),
+                                    i4_f16=to_np(qu.interleave_weight(qw.clone(), 4, "float16")),
+                                    i4_i8=to_np(qu.interleave_weight(qw.clone(), 4, "int8")),
+                                    i2_i8=to_np(qu.interleave_weight(qw.clone(), 2, "int8")))
+
     flat = {f"{case}/{key}": v for case, d in out.items() for key, v in d.items()}
     path = os.path.join(HERE, "reference_vectors.npz")
     np.savez_compressed(path, **flat)

@@ -70,3 +70,36 @@ def test_packing_helpers_match_oracle(golden):
     assert two_bit.shape == (5, 4)
     assert int(two_bit[0, 0]) == int(v[0, 0] | (v[0, 1] << 2) | (v[0, 2] << 4) | (v[0, 3] << 6))
     assert torch.equal(oc.unpack_uint4(q.pack_int4(torch.arange(16).view(1, 16))).view(-1), torch.arange(16, dtype=torch.uint8))
+
+
+def test_interleave_weight_matches_reference_vectors(golden):
+    """tilelang/quantize/utils.py:73-126, the (nbits, target) combinations that run in the reference."""
+    from tilelang_ascend_b200 import quantize as qz
+    from oracle import qgemm_oracle as oc
+    c = golden.case("interleave_weight")
+    qw = c["qweight"]
+    assert torch.equal(qz.interleave_weight(qw, 4, "float16"), c["i4_f16"])
+    assert torch.equal(qz.interleave_weight(qw, 4, "int8"), c["i4_i8"])
+    assert torch.equal(qz.interleave_weight(qw, 2, "int8"), c["i2_i8"])
+    assert torch.equal(oc.interleave_int4_f16_ref(qw.view(torch.uint8)), c["i4_f16"].view(torch.uint8))
+    assert torch.equal(qz.deinterleave_weight_int4_f16(c["i4_f16"]), qw.view(torch.uint8))
+    for nbits, tgt in ((1, "int8"), (1, "float16"), (2, "float16")):  # run here; they raise in the reference
+        out = qz.interleave_weight(qw, nbits, tgt)
+        assert out.shape == qw.shape and out.dtype == torch.int8
+    with pytest.raises(ValueError):
+        qz.interleave_weight(qw, 3, "float16")
+
+
+def test_group_quantiser_matches_reference_vector(golden):
+    """gen_quant4 (tilelang/quantize/utils.py:5-50): scales, integers and dequantised weights."""
+    from tilelang_ascend_b200 import quantize as qz
+    c = golden.case("gen_quant4")
+    torch.manual_seed(0)
+    original_w, linear, s, centred = qz.gen_quant4(256, 16, 128)
+    assert torch.equal(s, c["s"]) and torch.equal(centred.to(torch.int8), c["q_minus8"])
+    assert torch.equal(linear.weight.data, c["ref_weight_nk"])
+    q, s2 = qz.quantize_int4_groupwise(original_w, 128)
+    assert torch.equal(s2, s) and int(q.max()) <= 15 and int(q.min()) >= 0
+    assert torch.equal(q.to(torch.int32), torch.clamp(centred + 8, 0, 15))
+    z = qz.unpack_qzeros(qz.pack_int4(torch.tensor([[1, 15, 8, 0]])), 4)
+    assert torch.equal(z, torch.tensor([[1, 15, 8, 0]], dtype=torch.float16))

@@ -19,7 +19,15 @@ from .ops import (  # noqa: F401
     w4a16_gemm,
     w4a8_gemm_cv,
 )
-from .quantize import general_compress, pack_int4  # noqa: F401
+from .quantize import (  # noqa: F401
+    deinterleave_weight_int4_f16,
+    gen_quant4,
+    general_compress,
+    interleave_weight,
+    pack_int4,
+    quantize_int4_groupwise,
+    unpack_qzeros,
+)
 from ._lib import QGemmError  # noqa: F401
 
 __version__ = "0.1.0"

@@ -43,6 +43,10 @@ SIGNATURES = {
     "qgemm_w4a16_batched": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p,
                                        _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
                                        _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
+    "qgemm_w4a16_ex_workspace_bytes": (_c.c_int64, [_c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int]),
+    "qgemm_w4a16_ex": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
+                                  _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
+                                  _c.c_int64, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
     "qgemm_w4a16_noalloc": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p,
                                        _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_void_p,
                                        _c.c_void_p]),

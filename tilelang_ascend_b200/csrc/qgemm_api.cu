@@ -401,7 +401,7 @@ int64_t w4_gemm_min_m() {
 }
 bool w4_use_f16_gemm(int64_t M, int64_t N) { return M >= w4_gemm_min_m() && (N % 16) == 0; }
 
-int64_t qgemm_w4a16_batched_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K) {
+static int64_t w4_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K, bool dequant_once) {
   int sms = 0;
   if (ensure_device(&sms)) return -1;
   const int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
@@ -410,7 +410,15 @@ int64_t qgemm_w4a16_batched_workspace_bytes(int64_t batch, int64_t M, int64_t N,
   // [MT][128] fp32 per CTA, then the f16 copy of the activations in the kernel's K order
   // ... and, for the large-token path, the dequantised f16 weights
   return kW4CounterBytes + grid * 2 * (int64_t)mt * 128 * 4 + batch * M * K * 2 +
-         (w4_use_f16_gemm(M, N) ? batch * N * K * 2 : 0);
+         ((dequant_once || w4_use_f16_gemm(M, N)) ? batch * N * K * 2 : 0);
+}
+
+int64_t qgemm_w4a16_batched_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K) {
+  return w4_workspace_bytes(batch, M, N, K, false);
+}
+
+int64_t qgemm_w4a16_ex_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K, int has_zeros_tensor) {
+  return w4_workspace_bytes(batch, M, N, K, has_zeros_tensor != 0);
 }
 
 int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
@@ -479,9 +487,41 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
                              out_dtype, status, stream);
 }
 
+static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
+                      void* workspace, int64_t workspace_bytes, int64_t batch, int64_t M, int64_t N, int64_t K,
+                      int a_dtype, int out_dtype, uint32_t* status, void* stream, const void* zeros, int zero_mode,
+                      int weight_format);
+
 int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
                         void* workspace, int64_t workspace_bytes, int64_t batch, int64_t M, int64_t N, int64_t K,
                         int a_dtype, int out_dtype, uint32_t* status, void* stream) {
+  return w4a16_impl(A, B_packed, scales, zero, group, C, workspace, workspace_bytes, batch, M, N, K, a_dtype, out_dtype,
+                    status, stream, nullptr, QGEMM_ZERO_ORIGINAL, QGEMM_W4_SEQUENTIAL);
+}
+
+int qgemm_w4a16_ex(const void* A, const uint8_t* B_packed, const void* scales, const void* zeros, int zero,
+                   int zero_mode, int weight_format, int64_t group, void* C, void* workspace, int64_t workspace_bytes,
+                   int64_t batch, int64_t M, int64_t N, int64_t K, int a_dtype, int out_dtype, uint32_t* status,
+                   void* stream) {
+  if (weight_format != QGEMM_W4_SEQUENTIAL && weight_format != QGEMM_W4_INTERLEAVED_F16)
+    return fail("qgemm_w4a16_ex: unknown weight_format %d", weight_format);
+  if (zero_mode != QGEMM_ZERO_ORIGINAL && zero_mode != QGEMM_ZERO_RESCALE && zero_mode != QGEMM_ZERO_QUANTIZED)
+    return fail("qgemm_w4a16_ex: unknown zero_mode %d", zero_mode);
+  if (zeros == nullptr && zero_mode == QGEMM_ZERO_RESCALE)
+    return fail("qgemm_w4a16_ex: zero mode 'rescale' needs the zeros tensor");
+  if (zeros != nullptr) {
+    if (scales == nullptr) return fail("qgemm_w4a16_ex: a zeros tensor needs scales");
+    if (!aligned16(zeros)) return fail("qgemm_w4a16_ex: zeros must be 16-byte aligned");
+    if (N % 16 != 0) return fail("qgemm_w4a16_ex: a zeros tensor needs N to be a multiple of 16 (got %lld)", (long long)N);
+  }
+  return w4a16_impl(A, B_packed, scales, zero, group, C, workspace, workspace_bytes, batch, M, N, K, a_dtype, out_dtype,
+                    status, stream, zeros, zero_mode, weight_format);
+}
+
+static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
+                      void* workspace, int64_t workspace_bytes, int64_t batch, int64_t M, int64_t N, int64_t K,
+                      int a_dtype, int out_dtype, uint32_t* status, void* stream, const void* zeros, int zero_mode,
+                      int weight_format) {
   if (batch <= 0 || batch > 65535) return fail("qgemm_w4a16: batch must be in 1..65535 (got %lld)", (long long)batch);
   if (M <= 0 || N <= 0 || K <= 0) return fail("qgemm_w4a16: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M, (long long)N, (long long)K);
   if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return fail("qgemm_w4a16: dimension too large");
@@ -500,7 +540,8 @@ int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scal
     zero = 0;
     group = K;
   }
-  const int64_t need = qgemm_w4a16_batched_workspace_bytes(batch, M, N, K);
+  const bool dequant_once = zeros != nullptr || w4_use_f16_gemm(M, N);
+  const int64_t need = w4_workspace_bytes(batch, M, N, K, zeros != nullptr);
   if (need < 0) return -1;
   if (workspace == nullptr || workspace_bytes < need) return fail("qgemm_w4a16: workspace of %lld bytes needed (got %lld)", (long long)need, (long long)workspace_bytes);
 
@@ -564,10 +605,11 @@ int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scal
     if (blocks > 0x7fffffffll) return fail("qgemm_w4a16: activation tensor too large");
     qg::w4a16_prepare_activations<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint4*>(A),
                                                                   reinterpret_cast<uint4*>(a_prepared), n_chunks,
-                                                                  a_dtype == QGEMM_DT_BF16 ? 1 : 0);
+                                                                  a_dtype == QGEMM_DT_BF16 ? 1 : 0,
+                                                                  weight_format == QGEMM_W4_SEQUENTIAL ? 1 : 0);
     CUDA_OK(cudaGetLastError());
   }
-  if (w4_use_f16_gemm(M, N)) {
+  if (dequant_once) {
     uint8_t* w16 = a_prepared + batch * M * K * 2;
     const int64_t geff = group > K ? K : group;
     const long long n_chunks = (long long)batch * N * (K / 32);
@@ -575,6 +617,7 @@ int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scal
     if (blocks > 0x7fffffffll) return fail("qgemm_w4a16: weight tensor too large");
     qg::w4a16_dequant_weights<<<(unsigned)blocks, 256, 0, s>>>(reinterpret_cast<const uint4*>(B_packed),
                                                              static_cast<const __half*>(scales),
+                                                             static_cast<const __half*>(zeros), zero_mode,
                                                              reinterpret_cast<uint4*>(w16), n_chunks, (int)(K / 32),
                                                              (int)N, (int)K, (int)geff, zero);
     CUDA_OK(cudaGetLastError());

@@ -153,8 +153,9 @@ __device__ __forceinline__ uint4 w4_permute_act(uint4 v) {
 // what w4a16_prepare_activations gives the activations), same values as the GEMM kernels' in-flight
 // conversion.  One 16-byte packed chunk (32 weights -> 64 bytes) per thread, consecutive threads along K.
 __global__ void __launch_bounds__(256)
-w4a16_dequant_weights(const uint4* __restrict__ packed, const __half* __restrict__ scales, uint4* __restrict__ out,
-                      long long n_chunks, int chunks_per_row, int N, int K, int group, int zero) {
+w4a16_dequant_weights(const uint4* __restrict__ packed, const __half* __restrict__ scales,
+                      const __half* __restrict__ zeros, int zero_mode, uint4* __restrict__ out, long long n_chunks,
+                      int chunks_per_row, int N, int K, int group, int zero) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_chunks) return;
   const long long row = i / chunks_per_row;  // batch * N + n
@@ -172,10 +173,34 @@ w4a16_dequant_weights(const uint4* __restrict__ packed, const __half* __restrict
     s2 = (uint32_t)__half_as_ushort(scales[(b * (K / group) + g) * (long long)N + n]) * 0x00010001u;
   }
   uint32_t o[16];
-  w4_dequant8(v.x, sub_lo, sub_hi, s2, scaled, o + 0);
-  w4_dequant8(v.y, sub_lo, sub_hi, s2, scaled, o + 4);
-  w4_dequant8(v.z, sub_lo, sub_hi, s2, scaled, o + 8);
-  w4_dequant8(v.w, sub_lo, sub_hi, s2, scaled, o + 12);
+  if (zeros == nullptr) {
+    w4_dequant8(v.x, sub_lo, sub_hi, s2, scaled, o + 0);
+    w4_dequant8(v.y, sub_lo, sub_hi, s2, scaled, o + 4);
+    w4_dequant8(v.z, sub_lo, sub_hi, s2, scaled, o + 8);
+    w4_dequant8(v.w, sub_lo, sub_hi, s2, scaled, o + 12);
+  } else {
+    // Per-(group, column) zero points (tilelang/quantize/lop3.py:135-175, 232-270, 325-358).  The raw nibble
+    // values come out exact; then mode 0 / 2 ("original" / "quantized"): (q - z) * s, two roundings as the
+    // reference's sub.f16x2 + fma; mode 1 ("rescale"): fma(q, s, -|z|), one rounding.
+    const long long b = row / N;
+    const int n = (int)(row - b * N);
+    const uint32_t z2 = (uint32_t)__half_as_ushort(zeros[(b * (K / group) + k0 / group) * (long long)N + n]) * 0x00010001u;
+    const uint32_t raw_lo = 0x6400u * 0x00010001u, raw_hi = (0x5400u | 0x8000u) * 0x00010001u;
+    w4_dequant8(v.x, raw_lo, raw_hi, s2, false, o + 0);
+    w4_dequant8(v.y, raw_lo, raw_hi, s2, false, o + 4);
+    w4_dequant8(v.z, raw_lo, raw_hi, s2, false, o + 8);
+    w4_dequant8(v.w, raw_lo, raw_hi, s2, false, o + 12);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (zero_mode == 1) {
+        const uint32_t nz = z2 | 0x80008000u;  // -|z|, as the reference forms it (lop3.py:247)
+        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(o[j]) : "r"(o[j]), "r"(s2), "r"(nz));
+      } else {
+        asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(o[j]) : "r"(o[j]), "r"(z2));
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(o[j]) : "r"(o[j]), "r"(s2));
+      }
+    }
+  }
   uint4* dst = out + i * 4;
 #pragma unroll
   for (int j = 0; j < 4; ++j) __stcs(dst + j, make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]));
@@ -184,7 +209,8 @@ w4a16_dequant_weights(const uint4* __restrict__ packed, const __half* __restrict
 // Pre-pass: activations [M, K] (f16 or bf16) -> f16 with every group of eight K values reordered to
 // 0,4,1,5,2,6,3,7.  One 16-byte chunk per thread.
 __global__ void __launch_bounds__(256)
-w4a16_prepare_activations(const uint4* __restrict__ in, uint4* __restrict__ out, long long n_chunks, int is_bf16) {
+w4a16_prepare_activations(const uint4* __restrict__ in, uint4* __restrict__ out, long long n_chunks, int is_bf16,
+                          int permute) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_chunks) return;
   uint4 v = in[i];
@@ -194,7 +220,8 @@ w4a16_prepare_activations(const uint4* __restrict__ in, uint4* __restrict__ out,
     v.z = w4_bf16x2_to_f16x2(v.z);
     v.w = w4_bf16x2_to_f16x2(v.w);
   }
-  out[i] = w4_permute_act(v);
+  // interleaved weights (every 32-bit word holding elements 0,2,4,6 | 1,3,5,7) decode in natural order
+  out[i] = permute ? w4_permute_act(v) : v;
 }
 
 __device__ __forceinline__ void w4_epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }

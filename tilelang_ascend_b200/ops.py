@@ -197,15 +197,19 @@ def simple_quant_matmul(M: int, N: int, K: int, scale_size, block_M: int, block_
 _ws_cache = {}
 
 
-def _w4a16_workspace(lib, batch, M, N, K, device, stream_handle):
+_ZERO_MODES = {"original": 0, "rescale": 1, "quantized": 2}
+_WEIGHT_LAYOUTS = {"sequential": 0, "interleaved": 1}
+
+
+def _w4a16_workspace(lib, batch, M, N, K, device, stream_handle, zeros_tensor=False):
     """Scratch buffer (split-K partial sums + arrival counters + prepared activations), one per
     (device, stream), grown on demand.
 
     The counters must start at zero and the kernel leaves them zero, so the buffer is zeroed once, at
     creation.  Launches on different streams get different buffers because they may overlap on the GPU."""
-    need = lib.qgemm_w4a16_batched_workspace_bytes(batch, M, N, K)
+    need = lib.qgemm_w4a16_ex_workspace_bytes(batch, M, N, K, 1 if zeros_tensor else 0)
     if need < 0:
-        raise _lib.QGemmError("qgemm_w4a16_batched_workspace_bytes: " + _lib.last_error())
+        raise _lib.QGemmError("qgemm_w4a16_ex_workspace_bytes: " + _lib.last_error())
     key = (device.index, stream_handle)
     ws = _ws_cache.get(key)
     if ws is None or ws.numel() < need:
@@ -214,9 +218,15 @@ def _w4a16_workspace(lib, batch, M, N, K, device, stream_handle):
     return ws, need
 
 
-def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None, stream=None, status=None):
+def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None, stream=None, status=None,
+               zeros_mode="original", weight_layout="sequential"):
     """``C[M,N] = A[M,K] @ W[N,K].T`` with ``W = (unpack_u4(B_packed) - zeros).half() * scales[k // g, n]``
     (or the raw nibble values when ``scales is None``).  CUDA tensors in, CUDA tensor out.
+
+    ``zeros`` is an integer zero point or an fp16 tensor ``[K/g, N]`` of per-(group, feature) zero points;
+    ``zeros_mode`` is one of the reference's three (tilelang/quantize/lop3.py:1097): "original" ``(q - z) * s``,
+    "rescale" ``q * s - |z|``, "quantized" ``(q - qz) * s`` with integer ``qz`` (see ``quantize.unpack_qzeros``).
+    ``weight_layout="interleaved"`` takes weights permuted by ``interleave_weight(qweight, 4, "float16")``.
 
     Batched form: ``A[Batch,M,K]``, ``B_packed[Batch,N,K/2]``, ``scales[Batch,K/g,N]`` -> ``C[Batch,M,N]``,
     independent problems of one shape in a single launch (the batch dimension of ``simple_quant_batch_matmul``
@@ -240,23 +250,36 @@ def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None
     _check_tensor(B_packed, 1, "B_packed", torch.uint8, lead + (N, K // 2), dev)
     if K % 2 != 0:
         raise ValueError("K must be divisible by 2 (INT4 packed format)")
+    if zeros_mode not in _ZERO_MODES:
+        raise ValueError(f"zeros_mode must be one of {sorted(_ZERO_MODES)}, got {zeros_mode!r}")
+    if weight_layout not in _WEIGHT_LAYOUTS:
+        raise ValueError(f"weight_layout must be one of {sorted(_WEIGHT_LAYOUTS)}, got {weight_layout!r}")
+    zeros_t = None
     if scales is not None:
-        if not isinstance(zeros, int):
-            raise ValueError("zeros must be an integer zero point")
         if group_size in (-1, None):
             group_size = K
         if K % group_size != 0:
             raise ValueError("group_size must divide K")
         _check_tensor(scales, 2, "scales", torch.float16, lead + (K // group_size, N), dev)
+        if isinstance(zeros, torch.Tensor):
+            _check_tensor(zeros, 3, "zeros", torch.float16, lead + (K // group_size, N), dev)
+            zeros_t, zeros = zeros, 0
+        elif not isinstance(zeros, int):
+            raise ValueError("zeros must be an integer zero point or an fp16 tensor [K/g, N]")
+        elif zeros_mode == "rescale":
+            raise ValueError("zeros_mode 'rescale' needs a zeros tensor")
     else:
+        if isinstance(zeros, torch.Tensor):
+            raise ValueError("a zeros tensor needs scales")
         zeros, group_size = 0, K
     sh = _stream_handle(stream, dev)
     C = torch.empty(lead + (M, N), dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
-        ws, need = _w4a16_workspace(lib, batch, M, N, K, dev, sh)
-        rc = lib.qgemm_w4a16_batched(A.data_ptr(), B_packed.data_ptr(), _ptr(scales), int(zeros), int(group_size),
-                                     C.data_ptr(), ws.data_ptr(), need, batch, M, N, K, _ABI_DT[A.dtype],
-                                     _ABI_DT[out_dtype], _ptr(status), sh)
+        ws, need = _w4a16_workspace(lib, batch, M, N, K, dev, sh, zeros_t is not None)
+        rc = lib.qgemm_w4a16_ex(A.data_ptr(), B_packed.data_ptr(), _ptr(scales), _ptr(zeros_t), int(zeros),
+                                _ZERO_MODES[zeros_mode], _WEIGHT_LAYOUTS[weight_layout], int(group_size),
+                                C.data_ptr(), ws.data_ptr(), need, batch, M, N, K, _ABI_DT[A.dtype],
+                                _ABI_DT[out_dtype], _ptr(status), sh)
     _lib.check(rc, "qgemm_w4a16")
     return C
 
