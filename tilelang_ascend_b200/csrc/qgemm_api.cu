@@ -11,6 +11,7 @@
 #include "w4a16.cuh"
 #include "w4a16_decode.cuh"
 #include "act_quant.cuh"
+#include "w4a8.cuh"
 #include "w8a8.cuh"
 
 namespace {
@@ -78,6 +79,13 @@ int set_smem_w8_pair() {
   return 0;
 }
 template <int MT>
+int set_smem_w4i8() {
+  using C = qg::W4I8Cfg<MT>;
+  if (set_smem(qg::w4a8_gemm_kernel<MT, false>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a8_gemm_kernel<MT, true>, C::SMEM_BYTES)) return -1;
+  return 0;
+}
+template <int MT>
 int set_smem_w4() {
   using C = qg::W4Cfg<MT>;
   if (set_smem(qg::w4a16_gemm_kernel<MT, false>, C::SMEM_BYTES)) return -1;
@@ -105,6 +113,7 @@ int ensure_device(int* sm_count) {
     }
     if (set_smem_w8<128>() || set_smem_w8<256>() || set_smem_w8_pair()) return -1;
     if (set_smem_w4<16>() || set_smem_w4<32>() || set_smem_w4<64>() || set_smem_w4<128>()) return -1;
+    if (set_smem_w4i8<16>() || set_smem_w4i8<32>() || set_smem_w4i8<64>() || set_smem_w4i8<128>()) return -1;
     if (set_smem_w4d<0>() || set_smem_w4d<1>() || set_smem_w4d<2>() || set_smem_w4d<4>()) return -1;
     st.sm_count = prop.multiProcessorCount;
     st.ready = true;
@@ -233,6 +242,74 @@ __global__ void unpack_int4_kernel(const uint8_t* __restrict__ packed, int8_t* _
 }
 
 }  // namespace
+
+template <int MT>
+static int launch_w4i8(bool sgn, const CUtensorMap& tmW, const CUtensorMap& tmA, const qg::W4A8Params& p, int grid,
+                       cudaStream_t s) {
+  if (sgn) qg::w4a8_gemm_kernel<MT, true><<<grid, qg::W4_THREADS, qg::W4I8Cfg<MT>::SMEM_BYTES, s>>>(tmW, tmA, p);
+  else qg::w4a8_gemm_kernel<MT, false><<<grid, qg::W4_THREADS, qg::W4I8Cfg<MT>::SMEM_BYTES, s>>>(tmW, tmA, p);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Fused path of qgemm_w4a8 for up to 128 tokens: no int8 copy of the weights; the caller's [N, K] workspace
+// only holds the small scratch (arrival counters, int32 partial sums, reordered activations, row sums).
+// Returns 1 when the problem does not qualify (the caller then takes the two-kernel path).
+static int w4a8_fused(const int8_t* A, const uint8_t* qB, int8_t* workspace, int* C, int64_t M, int64_t N, int64_t K,
+                      int signed_nibbles, uint32_t* status, cudaStream_t s) {
+  static const int enabled = getenv("QGEMM_W4A8_FUSED") ? atoi(getenv("QGEMM_W4A8_FUSED")) : 1;
+  if (!enabled || M > 128 || !aligned16(workspace)) return 1;
+  int sms = 0;
+  if (ensure_device(&sms)) return -1;
+  const int mt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  const int64_t grid_max = sms < kW4MaxGrid ? sms : kW4MaxGrid;
+  const int64_t partial_bytes = grid_max * 2 * (int64_t)mt * 128 * 4;
+  const int64_t a_bytes = ((M * K + 255) / 256) * 256;
+  const int64_t need = kW4CounterBytes + partial_bytes + a_bytes + ((M * 4 + 255) / 256) * 256;
+  if (need > N * K) return 1;  // the caller's workspace is [N, K] int8
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  uint8_t* a_prepared = ws + kW4CounterBytes + partial_bytes;
+  int* row_sums = reinterpret_cast<int*>(a_prepared + a_bytes);
+
+  CUtensorMap tmW, tmA;
+  {
+    const uint64_t dims[2] = {(uint64_t)(K / 2), (uint64_t)N};
+    const uint64_t str[1] = {(uint64_t)(K / 2)};
+    const uint32_t box[2] = {128, 128};
+    if (encode_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, qB, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t str[1] = {(uint64_t)K};
+    const uint32_t box[2] = {128, (uint32_t)mt};
+    if (encode_map(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a_prepared, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+  }
+  qg::W4A8Params p;
+  p.C = C;
+  p.ws_counters = reinterpret_cast<uint32_t*>(ws);
+  p.ws_partials = reinterpret_cast<int*>(ws + kW4CounterBytes);
+  p.row_sums = row_sums;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.n_tiles = (int)((N + 127) / 128);
+  p.KS = (int)((K + 255) / 256);
+  p.total_items = (long long)p.n_tiles * p.KS;
+  p.status = status;
+  p.wait_limit_ns = g_wait_limit_ns;
+  int64_t grid = grid_max < p.total_items ? grid_max : p.total_items;
+  CUDA_OK(cudaMemsetAsync(ws, 0, kW4CounterBytes, s));  // the caller's buffer holds anything: counters start at zero
+  qg::w4a8_prepare_activations<<<(unsigned)M, 256, 0, s>>>(reinterpret_cast<const uint2*>(A),
+                                                          reinterpret_cast<uint2*>(a_prepared), row_sums, (int)K);
+  CUDA_OK(cudaGetLastError());
+  const bool sgn = signed_nibbles != 0;
+  switch (mt) {
+    case 16: return launch_w4i8<16>(sgn, tmW, tmA, p, (int)grid, s);
+    case 32: return launch_w4i8<32>(sgn, tmW, tmA, p, (int)grid, s);
+    case 64: return launch_w4i8<64>(sgn, tmW, tmA, p, (int)grid, s);
+    default: return launch_w4i8<128>(sgn, tmW, tmA, p, (int)grid, s);
+  }
+}
 
 extern "C" {
 
@@ -695,6 +772,12 @@ int qgemm_w4a8(const int8_t* A, const uint8_t* qB, int8_t* workspace, void* C, i
                int signed_nibbles, int out_dtype, uint32_t* status, void* stream) {
   if (workspace == nullptr) return fail("qgemm_w4a8: the int8 [N, K] workspace must not be null");
   if (K % 32 != 0 || N % 16 != 0) return fail("qgemm_w4a8: K must be a multiple of 32 and N of 16 (got K=%lld, N=%lld)", (long long)K, (long long)N);
+  if (out_dtype == QGEMM_DT_I32 && M > 0 && N > 0 && K > 0 && A != nullptr && qB != nullptr && C != nullptr &&
+      aligned16(A) && aligned16(qB) && aligned16(C)) {
+    const int rc = w4a8_fused(A, qB, workspace, static_cast<int*>(C), M, N, K, signed_nibbles, status,
+                              static_cast<cudaStream_t>(stream));
+    if (rc <= 0) return rc;
+  }
   if (qgemm_unpack_int4(qB, workspace, N, K, signed_nibbles, stream)) return -1;
   if (out_dtype == QGEMM_DT_I32)
     return qgemm_w8a8(A, workspace, nullptr, nullptr, C, nullptr, 1, M, N, K, 1, 0, QGEMM_DT_I32, QGEMM_B_NK, status, stream);

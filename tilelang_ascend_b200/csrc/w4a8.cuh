@@ -1,0 +1,428 @@
+// Fused W4A8 GEMM for sm_100a: C[m,n] = sum_k int32(A[m,k]) * int32(unpack(qB)[n,k]), exact, for up to 128 tokens.
+//
+// The int4 weights go from HBM to the tensor core without an int8 copy in global memory: the reference
+// (examples/dequantize_gemm/example_dequant_gemm_w4a8.py:69-119) and the two-kernel path of this library
+// unpack into an [N, K] int8 workspace first, 0.5 + 1 + 1 bytes of traffic per weight instead of 0.5.
+// Same pipeline as the W4A16 kernel in w4a16.cuh (TMA ring of packed slabs -> unpack warps -> tcgen05.st into a
+// ring of TMEM columns -> tcgen05.mma with the A operand from TMEM -> stream-K epilogue), with kind::i8 MMAs
+// (32 k per instruction), int32 accumulators and partial sums, and a three-instruction unpack per eight
+// weights, which leaves the kernel bound by the weight stream.
+#pragma once
+
+#include "common.cuh"
+#include "w4a16.cuh"
+
+namespace qg {
+
+struct W4A8Params {
+  int* C;                // [M, N] int32
+  int* ws_partials;      // scratch: 2 * grid slots of [MT][128] int32
+  uint32_t* ws_counters; // scratch: grid counters, zero on entry, left zero on exit
+  const int* row_sums;   // [M] sum_k A[m,k] (signed nibbles only)
+  int M, N, K;
+  int n_tiles;           // 128-row weight tiles; one token tile (M <= MT)
+  int KS;                // 256-wide K slabs per tile
+  long long total_items;
+  uint32_t* status;
+  unsigned long long wait_limit_ns;
+};
+
+constexpr int W4I8_W_COLS = W4_SLAB_K / 4;  // TMEM columns per slab of int8 weights (4 per 32-bit column)
+
+template <int MT>
+struct W4I8Cfg {
+  static constexpr int RAW_STAGES = 8;
+  static constexpr int A_STAGES = (MT <= 32) ? 8 : (MT == 64 ? 4 : 3);
+  static constexpr int MMAW = (MT <= 32) ? 4 : (MT == 64 ? 2 : 1);
+  static constexpr int W_STAGES = 4;
+  static constexpr int A_KB_BYTES = MT * 128;          // one 128-wide K block of int8 activations
+  static constexpr int A_BYTES = 2 * A_KB_BYTES;       // one 256-wide slab
+  static constexpr int ACC_COLS = 2 * MMAW * MT;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int SMEM_BYTES = RAW_STAGES * W4_RAW_PACKED + A_STAGES * A_BYTES + BAR_BYTES + 1024;
+  static constexpr int CH = (MT < 32) ? 16 : 32;
+  static_assert(ACC_COLS + W_STAGES * W4I8_W_COLS <= 512, "tensor memory budget");
+};
+
+// Pre-pass: int8 activations [M, K] -> the same values with every group of eight k reordered to
+// 0,2,4,6,1,3,5,7 (the byte order the unpack produces), and the row sums.  One block per row.
+__global__ void __launch_bounds__(256)
+w4a8_prepare_activations(const uint2* __restrict__ in, uint2* __restrict__ out, int* __restrict__ row_sums, int K) {
+  __shared__ int red[8];
+  const int m = blockIdx.x;
+  const uint2* src = in + (size_t)m * (K / 8);
+  uint2* dst = out + (size_t)m * (K / 8);
+  int acc = 0;
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+    const uint2 v = src[i];
+    acc = __dp4a((int)v.x, 0x01010101, acc);
+    acc = __dp4a((int)v.y, 0x01010101, acc);
+    dst[i] = make_uint2(__byte_perm(v.x, v.y, 0x6420), __byte_perm(v.x, v.y, 0x7531));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int s = 0;
+    for (int w = 0; w < 8; ++w) s += red[w];
+    row_sums[m] = s;
+  }
+}
+
+template <int MT, bool SIGNED>
+__global__ void __launch_bounds__(W4_THREADS, 1)
+w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
+                 const W4A8Params p) {
+  using Cfg = W4I8Cfg<MT>;
+  constexpr int RS = Cfg::RAW_STAGES;
+  constexpr int AS = Cfg::A_STAGES;
+  constexpr int WS = Cfg::W_STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* raw_base = smem;
+  uint8_t* a_base = smem + RS * W4_RAW_PACKED;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(a_base + AS * Cfg::A_BYTES);
+  uint64_t* raw_full = bars;
+  uint64_t* raw_empty = raw_full + RS;
+  uint64_t* a_full = raw_empty + RS;
+  uint64_t* a_empty = a_full + AS;
+  uint64_t* w_full = a_empty + AS;
+  uint64_t* w_empty = w_full + WS;
+  uint64_t* tfull = w_empty + WS;
+  uint64_t* tempty = tfull + 2;
+  uint64_t* drain = tempty + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* epi_flag = tmem_slot + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < RS; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], W4_DQ_WARPS);
+    }
+    for (int s = 0; s < AS; ++s) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&a_empty[s], Cfg::MMAW);
+    }
+    for (int s = 0; s < WS; ++s) {
+      mbar_init(&w_full[s], W4_DQ_WARPS);
+      mbar_init(&w_empty[s], Cfg::MMAW);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], Cfg::MMAW);
+      mbar_init(&tempty[i], 4);
+    }
+    mbar_init(drain, 1);
+    *abort_flag = 0;
+    *epi_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmA);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_w = tmem_base + Cfg::ACC_COLS;  // ring of dequantised-weight columns
+  const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns, 0};
+
+  const int G = gridDim.x;
+  const int cta = blockIdx.x;
+  const long long T = p.total_items;
+  W4SegIter seg{w4_range_begin(T, G, cta), w4_range_begin(T, G, cta + 1), p.KS};
+  int tile, ks0, ks1;
+
+  if (warp == 0) {
+    // ------------------------------------------- raw producer: packed weights + scales
+    if (lane == 0) {
+      int rs = 0;
+      uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
+      bool ok = true;
+      const uint32_t tx = W4_RAW_PACKED;
+      while (ok && seg.next(tile, ks0, ks1)) {
+        const int n0 = tile * W4_BN;
+        for (int ks = ks0; ks < ks1; ++ks) {
+          if (!mbar_wait(&raw_empty[rs], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* dst = raw_base + rs * W4_RAW_PACKED;
+          mbar_arrive_expect_tx(&raw_full[rs], tx);
+          tma_load_2d(dst, &tmW, &raw_full[rs], ks * (W4_SLAB_K / 2), n0);
+          issued_mask |= 1u << rs;
+          parity_mask = (parity_mask & ~(1u << rs)) | (phase << rs);
+          if (++rs == RS) { rs = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        for (int s = 0; s < RS; ++s) {
+          if (!(issued_mask & (1u << s))) continue;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(&raw_full[s], (parity_mask >> s) & 1u)) {
+            if (global_timer_ns() - t0 > p.wait_limit_ns) {
+              if (p.status) atomicMax(p.status, (uint32_t)ST_TIMEOUT_DRAIN);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------- activation producer
+    if (lane == 0) {
+      int as = 0;
+      uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
+      bool ok = true;
+      while (ok && seg.next(tile, ks0, ks1)) {
+        for (int ks = ks0; ks < ks1; ++ks) {
+          if (!mbar_wait(&a_empty[as], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* dstA = a_base + as * Cfg::A_BYTES;
+          mbar_arrive_expect_tx(&a_full[as], Cfg::A_BYTES);
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb)  // two 128-byte (128 k) blocks of int8 activations per slab
+            tma_load_2d(dstA + kb * Cfg::A_KB_BYTES, &tmA, &a_full[as], ks * W4_SLAB_K + kb * 128, 0);
+          issued_mask |= 1u << as;
+          parity_mask = (parity_mask & ~(1u << as)) | (phase << as);
+          if (++as == AS) { as = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        for (int s = 0; s < AS; ++s) {
+          if (!(issued_mask & (1u << s))) continue;
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(&a_full[s], (parity_mask >> s) & 1u)) {
+            if (global_timer_ns() - t0 > p.wait_limit_ns) {
+              if (p.status) atomicMax(p.status, (uint32_t)ST_TIMEOUT_DRAIN);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1 || warp >= W4_FIRST_XMMA_WARP) {
+    // -------------------------------------------------------------- MMA issuers
+    // Issuer w of MMAW takes the K steps kk = w, w + MMAW, ... of every slab and accumulates them into its
+    // own accumulator (columns w*MT of the buffer).
+    const int mw = (warp == 1) ? 0 : (warp - W4_FIRST_XMMA_WARP + 1);
+    if (mw < Cfg::MMAW && lane == 0) {
+      constexpr uint32_t idesc = make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, 0, W4_BN, MT);
+      const uint64_t desc_hi = make_desc_kmajor(0);  // K-major activation descriptor without its start address
+      const uint32_t a_base_u32 = smem_u32(a_base);
+      int ws = 0, as = 0;
+      uint32_t wphase = 0, aphase = 0;
+      int it = 0;
+      bool ok = true;
+      while (ok && seg.next(tile, ks0, ks1)) {
+        const int buf = it & 1;
+        const uint32_t tphase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d = tmem_base + buf * (Cfg::MMAW * MT) + mw * MT;
+        uint32_t started = 0;  // 0 for this issuer's first MMA of the segment: overwrite the accumulator
+        for (int ks = ks0; ks < ks1; ++ks) {
+          if (!mbar_wait(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+          if (!mbar_wait(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t adesc0 = desc_hi | (uint64_t)(((a_base_u32 + as * Cfg::A_BYTES) & 0x3FFFFu) >> 4);
+          const uint32_t tW = tmem_w + ws * W4I8_W_COLS;
+#pragma unroll
+          for (int j = 0; j < (W4_SLAB_K / 32) / Cfg::MMAW; ++j) {  // 32 k per MMA: 8 TMEM columns, 32 bytes of smem
+            const int kk = j * Cfg::MMAW + mw;
+            const uint32_t off = (uint32_t)(((kk >> 2) * Cfg::A_KB_BYTES + (kk & 3) * 32) >> 4);
+            umma_i8_ts(d, tW + kk * 8, adesc0 + off, idesc, started);
+            started = 1u;
+          }
+          umma_commit(&w_empty[ws]);
+          umma_commit(&a_empty[as]);
+          if (++ws == WS) { ws = 0; wphase ^= 1u; }
+          if (++as == AS) { as = 0; aphase ^= 1u; }
+        }
+        if (ok) umma_commit(&tfull[buf]);
+        ++it;
+      }
+      if (!ok && mw == 0) {
+        umma_commit(drain);
+        const uint64_t t0 = global_timer_ns();
+        while (!mbar_try_wait(drain, 0)) {
+          if (global_timer_ns() - t0 > p.wait_limit_ns) break;
+        }
+      }
+    }
+  } else if (warp >= 3 && warp < W4_FIRST_DQ_WARP) {
+    // ---------------------------------------------------------------- epilogue
+    // int32 accumulators: the MMAW accumulators add exactly; signed nibbles were fed as (value + 8), so
+    // 8 * sum_k a[m,k] comes off once, when the tile's full-K sum is written.
+    constexpr int CH = Cfg::CH;
+    const int q = warp & 3;
+    const int nl = q * 32 + lane;  // weight row inside the tile == TMEM lane
+    int it = 0;
+    while (seg.next(tile, ks0, ks1)) {
+      const int buf = it & 1;
+      const uint32_t tphase = (it >> 1) & 1;
+      ++it;
+      const int n = tile * W4_BN + nl;
+      const bool full_tile = (ks0 == 0 && ks1 == p.KS);
+      const int my_slot = (ks1 < p.KS) ? 2 * cta + 1 : 2 * cta;
+      const bool ok = mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE);
+      if (ok) {
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (Cfg::MMAW * MT);
+#pragma unroll 1
+        for (int c = 0; c < MT / CH; ++c) {
+          uint32_t r[CH];
+          if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + c * CH, r);
+          else tmem_ld_32x32b_x32(taddr + c * CH, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int a = 1; a < Cfg::MMAW; ++a) {
+            uint32_t r2[CH];
+            if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + a * MT + c * CH, r2);
+            else tmem_ld_32x32b_x32(taddr + a * MT + c * CH, r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < CH; ++j) r[j] += r2[j];
+          }
+          if (full_tile) {
+            if (n < p.N) {
+#pragma unroll
+              for (int j = 0; j < CH; ++j) {
+                const int m = c * CH + j;
+                if (m < p.M) p.C[(size_t)m * p.N + n] = (int)r[j] - (SIGNED ? 8 * __ldg(p.row_sums + m) : 0);
+              }
+            }
+          } else {
+            int* dst = p.ws_partials + (size_t)my_slot * (MT * W4_BN) + (size_t)(c * CH) * W4_BN + nl;
+#pragma unroll
+            for (int j = 0; j < CH; ++j) dst[j * W4_BN] = (int)r[j];
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[buf]);
+      }
+      if (full_tile) {
+        if (!ok) break;
+        continue;
+      }
+      // Split tile: publish the partial, count arrivals; the last contributor adds them up.
+      const long long first_item = (long long)tile * p.KS;
+      const int b_first = w4_owner(T, G, first_item);
+      const int b_last = w4_owner(T, G, first_item + p.KS - 1);
+      __threadfence();
+      w4_epi_bar();
+      if (warp == 3 && lane == 0) {
+        uint32_t last = 0;
+        if (!*abort_flag) {
+          const uint32_t old = atomicAdd(p.ws_counters + b_first, 1u);
+          if (old == (uint32_t)(b_last - b_first)) {
+            last = 1;
+            p.ws_counters[b_first] = 0;  // every contributor has arrived: leave the counter clean
+          }
+        }
+        *epi_flag = last;
+      }
+      w4_epi_bar();
+      const bool is_last = *epi_flag != 0;
+      const bool aborted = *abort_flag != 0;
+      w4_epi_bar();  // epi_flag may be rewritten only after everyone has read it
+      if (aborted) break;
+      if (is_last) {
+        __threadfence();
+        if (n < p.N) {
+          constexpr int RU = 16;
+          const int rows = min(MT, p.M);
+#pragma unroll 1
+          for (int mb = 0; mb < rows; mb += RU) {
+            int sum[RU];
+#pragma unroll
+            for (int u = 0; u < RU; ++u) sum[u] = 0;
+#pragma unroll 1
+            for (int c = b_first; c <= b_last; ++c) {
+              const long long c_end = w4_range_begin(T, G, c + 1);
+              const int slot = (c_end >= first_item + p.KS) ? 2 * c : 2 * c + 1;
+              const int* src = p.ws_partials + (size_t)slot * (MT * W4_BN) + (size_t)mb * W4_BN + nl;
+              int v[RU];
+#pragma unroll
+              for (int u = 0; u < RU; ++u) v[u] = (mb + u < rows) ? __ldcg(src + u * W4_BN) : 0;
+#pragma unroll
+              for (int u = 0; u < RU; ++u) sum[u] += v[u];
+            }
+#pragma unroll
+            for (int u = 0; u < RU; ++u) {
+              if (mb + u < rows)
+                p.C[(size_t)(mb + u) * p.N + n] = sum[u] - (SIGNED ? 8 * __ldg(p.row_sums + mb + u) : 0);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp >= W4_FIRST_DQ_WARP && warp < W4_FIRST_XMMA_WARP) {
+    // ----------------------------------------------------------------- unpack
+    // Warp (q, j): TMEM lanes 32q..32q+31, K sub-range [64j, 64j+64) of the slab = packed 16-byte chunks 2j and
+    // 2j+1 of the row = 64 int8 = 16 TMEM columns.  Word x holds nibbles n0..n7 of eight consecutive k:
+    // (x & 0x0f0f0f0f) = bytes (n0, n2, n4, n6), ((x >> 4) & 0x0f0f0f0f) = (n1, n3, n5, n7); the pre-pass stores
+    // the activations in that same order, so no byte shuffle is needed.  Two's-complement nibbles are biased
+    // by XOR 8 (value + 8 in 0..15) in the same lop3.
+    const int wd = warp - W4_FIRST_DQ_WARP;
+    const int q = warp & 3;
+    const int j = wd >> 2;
+    const int row = q * 32 + lane;
+    const int sw = row & 7;
+    const uint32_t off0 = row * 128 + (((2 * j) ^ sw) << 4);
+    const uint32_t off1 = row * 128 + (((2 * j + 1) ^ sw) << 4);
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    int rs = 0, ws = 0;
+    uint32_t rphase = 0, wphase = 0;
+    bool ok = true;
+    while (ok && seg.next(tile, ks0, ks1)) {
+      for (int ks = ks0; ks < ks1; ++ks) {
+        if (!mbar_wait_warp(&raw_full[rs], rphase, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
+        const uint8_t* rawp = raw_base + rs * W4_RAW_PACKED;
+        const uint4 v0 = *reinterpret_cast<const uint4*>(rawp + off0);
+        const uint4 v1 = *reinterpret_cast<const uint4*>(rawp + off1);
+        const uint32_t x[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        uint32_t o[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t y = x[i] >> 4;
+          if (SIGNED) {
+            asm("lop3.b32 %0, %1, 0x0f0f0f0f, 0x08080808, 0x6a;" : "=r"(o[2 * i]) : "r"(x[i]));
+            asm("lop3.b32 %0, %1, 0x0f0f0f0f, 0x08080808, 0x6a;" : "=r"(o[2 * i + 1]) : "r"(y));
+          } else {
+            o[2 * i] = x[i] & 0x0f0f0f0fu;
+            o[2 * i + 1] = y & 0x0f0f0f0fu;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[rs]);
+        if (++rs == RS) { rs = 0; rphase ^= 1u; }
+
+        if (!mbar_wait_warp(&w_empty[ws], wphase ^ 1u, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
+        tc_fence_after_sync();
+        tmem_st_32x32b_x16(tmem_w + lane_addr + ws * W4I8_W_COLS + j * 16, o);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&w_full[ws]);
+        if (++ws == WS) { ws = 0; wphase ^= 1u; }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace qg
