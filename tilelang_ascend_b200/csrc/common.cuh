@@ -124,6 +124,14 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, c
   return ok != 0;
 }
 
+// ------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start once every block of the
+// kernel in front of it has executed pdl_launch_dependents() (or exited); whatever it reads from that kernel
+// must come after pdl_wait(), which returns when the earlier kernel has completed and its writes are visible.
+// Both are no-ops when the launch carries no such dependency.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");

@@ -142,6 +142,26 @@ int encode_map(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* b
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Launch `kernel` so that it may start while the kernel in front of it on the stream is still running
+// (programmatic dependent launch); the kernel itself waits before it reads that kernel's results.
+// QGEMM_PDL=0 falls back to plain stream order.
+template <typename... KArgs, typename... Args>
+int launch_pdl(void (*kernel)(KArgs...), int grid, int threads, int smem, cudaStream_t s, Args&&... args) {
+  static const int pdl = getenv("QGEMM_PDL") ? atoi(getenv("QGEMM_PDL")) : 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...));
+  return 0;
+}
+
 template <int BN, bool NK, bool BF>
 int launch_w8(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const qg::W8A8Params& p, int grid,
               cudaStream_t s) {
@@ -160,23 +180,15 @@ int launch_w8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const qg::W8A
 template <int MT>
 int launch_w4(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
               const qg::W4A16Params& p, int grid, cudaStream_t s) {
-  if (bf)
-    qg::w4a16_gemm_kernel<MT, true><<<grid, qg::W4_THREADS, qg::W4Cfg<MT>::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
-  else
-    qg::w4a16_gemm_kernel<MT, false><<<grid, qg::W4_THREADS, qg::W4Cfg<MT>::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
-  CUDA_OK(cudaGetLastError());
-  return 0;
+  if (bf) return launch_pdl(qg::w4a16_gemm_kernel<MT, true>, grid, qg::W4_THREADS, qg::W4Cfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p);
+  return launch_pdl(qg::w4a16_gemm_kernel<MT, false>, grid, qg::W4_THREADS, qg::W4Cfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p);
 }
 
 template <int FLUSH, int NB>
 int launch_w4d_nb(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
                   const qg::W4A16Params& p, int grid, cudaStream_t s) {
-  if (bf)
-    qg::w4a16_decode_kernel<FLUSH, NB, true><<<grid, qg::W4D_THREADS, qg::W4DCfg<NB>::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
-  else
-    qg::w4a16_decode_kernel<FLUSH, NB, false><<<grid, qg::W4D_THREADS, qg::W4DCfg<NB>::SMEM_BYTES, s>>>(tmW, tmS, tmA, p);
-  CUDA_OK(cudaGetLastError());
-  return 0;
+  if (bf) return launch_pdl(qg::w4a16_decode_kernel<FLUSH, NB, true>, grid, qg::W4D_THREADS, qg::W4DCfg<NB>::SMEM_BYTES, s, tmW, tmS, tmA, p);
+  return launch_pdl(qg::w4a16_decode_kernel<FLUSH, NB, false>, grid, qg::W4D_THREADS, qg::W4DCfg<NB>::SMEM_BYTES, s, tmW, tmS, tmA, p);
 }
 template <int FLUSH>
 int launch_w4d(bool bf, int mt, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
@@ -246,10 +258,8 @@ __global__ void unpack_int4_kernel(const uint8_t* __restrict__ packed, int8_t* _
 template <int MT>
 static int launch_w4i8(bool sgn, const CUtensorMap& tmW, const CUtensorMap& tmA, const qg::W4A8Params& p, int grid,
                        cudaStream_t s) {
-  if (sgn) qg::w4a8_gemm_kernel<MT, true><<<grid, qg::W4_THREADS, qg::W4I8Cfg<MT>::SMEM_BYTES, s>>>(tmW, tmA, p);
-  else qg::w4a8_gemm_kernel<MT, false><<<grid, qg::W4_THREADS, qg::W4I8Cfg<MT>::SMEM_BYTES, s>>>(tmW, tmA, p);
-  CUDA_OK(cudaGetLastError());
-  return 0;
+  if (sgn) return launch_pdl(qg::w4a8_gemm_kernel<MT, true>, grid, qg::W4_THREADS, qg::W4I8Cfg<MT>::SMEM_BYTES, s, tmW, tmA, p);
+  return launch_pdl(qg::w4a8_gemm_kernel<MT, false>, grid, qg::W4_THREADS, qg::W4I8Cfg<MT>::SMEM_BYTES, s, tmW, tmA, p);
 }
 
 // Fused path of qgemm_w4a8 for up to 128 tokens: no int8 copy of the weights; the caller's [N, K] workspace
@@ -298,9 +308,10 @@ static int w4a8_fused(const int8_t* A, const uint8_t* qB, int8_t* workspace, int
   p.status = status;
   p.wait_limit_ns = g_wait_limit_ns;
   int64_t grid = grid_max < p.total_items ? grid_max : p.total_items;
-  CUDA_OK(cudaMemsetAsync(ws, 0, kW4CounterBytes, s));  // the caller's buffer holds anything: counters start at zero
   qg::w4a8_prepare_activations<<<(unsigned)M, 256, 0, s>>>(reinterpret_cast<const uint2*>(A),
-                                                          reinterpret_cast<uint2*>(a_prepared), row_sums, (int)K);
+                                                          reinterpret_cast<uint2*>(a_prepared), row_sums,
+                                                          reinterpret_cast<uint32_t*>(ws), (int)(kW4CounterBytes / 4),
+                                                          (int)K);
   CUDA_OK(cudaGetLastError());
   const bool sgn = signed_nibbles != 0;
   switch (mt) {

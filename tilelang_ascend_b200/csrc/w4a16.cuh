@@ -211,6 +211,7 @@ w4a16_dequant_weights(const uint4* __restrict__ packed, const __half* __restrict
 __global__ void __launch_bounds__(256)
 w4a16_prepare_activations(const uint4* __restrict__ in, uint4* __restrict__ out, long long n_chunks, int is_bf16,
                           int permute) {
+  pdl_launch_dependents();  // the GEMM kernel behind may set up and start streaming weights meanwhile
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_chunks) return;
   uint4 v = in[i];
@@ -338,6 +339,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   } else if (warp == 2) {
     // ------------------------------------------------- activation producer
     if (lane == 0) {
+      pdl_wait();  // the prepared activations come from the pre-pass kernel in front of this one
       int as = 0;
       uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
       bool ok = true;

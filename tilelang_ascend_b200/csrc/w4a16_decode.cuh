@@ -137,6 +137,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
       uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
       bool ok = true;
       const uint32_t tx = W4_RAW_PACKED + (SCALED ? p.scale_rows * 256 : 0) + 4 * Cfg::A_KB_BYTES;
+      bool waited = false;  // the activations come from the pre-pass kernel in front: wait for it once, after
+                            // the first weight loads are on their way
       while (ok && seg.next(tile, ks0, ks1)) {
         int b, n0, m0;
         w4_tile_coords(p, tile, MT, b, n0, m0);
@@ -149,6 +151,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             const int srow = (p.group <= W4_SLAB_K) ? ks * p.scale_rows : (ks * W4_SLAB_K) / p.group;
             tma_load_3d(dst + W4_RAW_PACKED, &tmS, &full[s], n0, srow, b);
           }
+          if (!waited) { pdl_wait(); waited = true; }
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb)
             tma_load_3d(dst + W4_RAW_BYTES + kb * Cfg::A_KB_BYTES, &tmA, &full[s], ks * W4_SLAB_K + kb * 64, m0, b);

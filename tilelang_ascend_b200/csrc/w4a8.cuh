@@ -48,8 +48,12 @@ struct W4I8Cfg {
 // Pre-pass: int8 activations [M, K] -> the same values with every group of eight k reordered to
 // 0,2,4,6,1,3,5,7 (the byte order the unpack produces), and the row sums.  One block per row.
 __global__ void __launch_bounds__(256)
-w4a8_prepare_activations(const uint2* __restrict__ in, uint2* __restrict__ out, int* __restrict__ row_sums, int K) {
+w4a8_prepare_activations(const uint2* __restrict__ in, uint2* __restrict__ out, int* __restrict__ row_sums,
+                         uint32_t* __restrict__ counters, int n_counters, int K) {
   __shared__ int red[8];
+  pdl_launch_dependents();
+  // the caller's scratch holds anything: the arrival counters start at zero
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_counters; i += gridDim.x * blockDim.x) counters[i] = 0u;
   const int m = blockIdx.x;
   const uint2* src = in + (size_t)m * (K / 8);
   uint2* dst = out + (size_t)m * (K / 8);
@@ -177,6 +181,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   } else if (warp == 2) {
     // ------------------------------------------------- activation producer
     if (lane == 0) {
+      pdl_wait();  // the reordered activations come from the pre-pass kernel in front of this one
       int as = 0;
       uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
       bool ok = true;
@@ -263,6 +268,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const int q = warp & 3;
     const int nl = q * 32 + lane;  // weight row inside the tile == TMEM lane
     int it = 0;
+    pdl_wait();  // row sums and zeroed counters come from the pre-pass kernel
     while (seg.next(tile, ks0, ks1)) {
       const int buf = it & 1;
       const uint32_t tphase = (it >> 1) & 1;
