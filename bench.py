@@ -327,6 +327,21 @@ def run_suite(q, world, rank, peaks):
                     "gbs": round(by / ms / 1e6, 1), "frac_of_measured_hbm": round(by / ms / 1e6 / peaks["hbm_gbs"], 4)})
         del X
 
+    if world == 1:
+        # fused W4A8 at decode size on the config-5 weight shape: signed int4 weights, int8 activations, int32 out
+        Kq, Nq, Mq = 8192, 28672, 16
+        gen = torch.Generator().manual_seed(6)
+        qBs = [torch.randint(0, 256, (Nq, Kq // 2), dtype=torch.uint8, generator=gen).cuda() for _ in range(2)]
+        A8 = torch.randint(-128, 128, (Mq, Kq), dtype=torch.int8, generator=gen).cuda()
+        wsq = torch.empty((Nq, Kq), dtype=torch.int8, device="cuda")
+        Cq = torch.empty((Mq, Nq), dtype=torch.int32, device="cuda")
+        kq = q.w4a8_gemm_cv(Mq, Nq, Kq)
+        ms = _time_rotating(lambda i: kq(A8, qBs[i % 2], wsq, Cq), 2, 20, world)
+        by = Nq * Kq // 2 + Mq * Kq + 4 * Mq * Nq
+        res.append({"config": f"W4A8 fused M={Mq} K={Kq} N={Nq} (signed int4 x int8 -> int32)", "ms": round(ms, 5),
+                    "gbs": round(by / ms / 1e6, 1), "frac_of_measured_hbm": round(by / ms / 1e6 / peaks["hbm_gbs"], 4)})
+        del qBs, wsq
+
     # config 4: batch sharded, no collective
     A, B, sa, sb = oc.make_config_inputs("cfg4")
     A, B, sa, sb = [t.cuda() for t in shard_batches([A, B, sa, sb], world, rank)]

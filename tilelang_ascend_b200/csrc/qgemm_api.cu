@@ -431,6 +431,17 @@ static int w8a8_impl(const int8_t* A, const int8_t* B, const float* scale_b, con
   p.status = status;
   p.wait_limit_ns = g_wait_limit_ns;
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);
+  // Tail split: when the last round of the persistent grid would run R < grid/2 tiles, those tiles are issued
+  // as 2R half-width items instead ([K, N] layout, 256-column tiles).
+  p.split_from = p.num_items = p.num_tiles;
+  {
+    static const int tail_split = getenv("QGEMM_W8_TAIL_SPLIT") ? atoi(getenv("QGEMM_W8_TAIL_SPLIT")) : 1;
+    const int64_t R = num_tiles % grid;
+    if (tail_split && b_layout == QGEMM_B_KN && BN == 256 && num_tiles > grid && R > 0 && 2 * R <= grid) {
+      p.split_from = (int)(num_tiles - R);
+      p.num_items = (int)(num_tiles + R);
+    }
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool nk = b_layout == QGEMM_B_NK;
   const bool bf = out_dtype == QGEMM_DT_BF16;
@@ -556,6 +567,7 @@ static int w4_f16_gemm(const void* A16, const void* W16, void* C, int64_t batch,
   p.status = status;
   p.wait_limit_ns = g_wait_limit_ns;
   p.tma_store = 1;
+  p.split_from = p.num_items = p.num_tiles;
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);
   if (BN == 256) {
     if (bf) qg::w8a8_gemm_kernel<256, true, true, true><<<grid, qg::W8_THREADS, qg::W8Cfg<256>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);

@@ -29,12 +29,16 @@ struct W8A8Params {
   // of the table is (group, first row, valid rows <= 128).  Null for the plain and batched forms.
   const int* meta;
   int groups;
+  // Tail split: work items from `split_from` on are half-width tiles (item split_from + 2i + h is the left or
+  // right half of tile split_from + i), so that the last, partly filled round of the persistent grid keeps
+  // twice as many SMs busy for about half as long.  num_items = num_tiles when nothing is split.
+  int split_from, num_items;
   int tma_store;  // C is written with tiled bulk stores from a shared-memory staging tile (needs bn % 64 == 0)
 };
 
 // One output tile's coordinates: batch index of B / scale_b, batch index of A / C / scale_a, first row, valid rows.
 struct W8Tile {
-  int bB, bA, m0, rows, n_blk;
+  int bB, bA, m0, rows, n0, bn;  // n0: first column, bn: columns of this item
 };
 
 constexpr int W8_BM = 128;      // tile rows (= MMA M, one TMEM lane per row)
@@ -69,11 +73,19 @@ __device__ __forceinline__ void w8_decode_tile(const W8A8Params& p, int tile, in
   n_blk = in_band / gsz;
 }
 
-__device__ __forceinline__ W8Tile w8_tile(const W8A8Params& p, int tile) {
+__device__ __forceinline__ W8Tile w8_tile(const W8A8Params& p, int item) {
   int b, m_blk, n_blk;
-  w8_decode_tile(p, tile, b, m_blk, n_blk);
   W8Tile t;
-  t.n_blk = n_blk;
+  if (item < p.split_from) {
+    w8_decode_tile(p, item, b, m_blk, n_blk);
+    t.n0 = n_blk * p.bn;
+    t.bn = p.bn;
+  } else {
+    const int h = item - p.split_from;
+    w8_decode_tile(p, p.split_from + (h >> 1), b, m_blk, n_blk);
+    t.bn = p.bn >> 1;
+    t.n0 = n_blk * p.bn + (h & 1) * t.bn;
+  }
   if (p.meta == nullptr) {
     t.bB = t.bA = b;
     t.m0 = m_blk * W8_BM;
@@ -147,21 +159,23 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      for (int tile = blockIdx.x; ok && tile < p.num_items; tile += gridDim.x) {
         const W8Tile t = w8_tile(p, tile);
-        const int m0 = t.m0, n0 = t.n_blk * p.bn;
+        const int m0 = t.m0, n0 = t.n0;
+        const int b_boxes = B_NK ? 1 : (t.bn + 127) / 128;  // 128-column boxes of B actually needed
+        const uint32_t tx = Cfg::A_BYTES + (B_NK ? (uint32_t)Cfg::B_BYTES : (uint32_t)(b_boxes * W8_BK * 128));
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           uint8_t* sA = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sB = sA + Cfg::A_BYTES;
-          mbar_arrive_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          mbar_arrive_expect_tx(&full[stage], tx);
           tma_load_3d(sA, &tmA, &full[stage], kb * W8_BK, m0, t.bA);
           if constexpr (B_NK) {
             tma_load_3d(sB, &tmB, &full[stage], kb * W8_BK, n0, t.bB);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 128; ++c)
-              tma_load_3d(sB + c * (W8_BK * 128), &tmB, &full[stage], n0 + c * 128, kb * W8_BK, t.bB);
+              if (c < b_boxes) tma_load_3d(sB + c * (W8_BK * 128), &tmB, &full[stage], n0 + c * 128, kb * W8_BK, t.bB);
           }
           issued_mask |= 1u << stage;
           parity_mask = (parity_mask & ~(1u << stage)) | (phase << stage);
@@ -185,13 +199,14 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = F16 ? make_idesc(ACC_F32, FMT_F16, FMT_F16, 0, B_NK ? 0 : 1, W8_BM, (uint32_t)p.bn)
-                                 : make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, B_NK ? 0 : 1, W8_BM, (uint32_t)p.bn);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
+      for (int tile = blockIdx.x; ok && tile < p.num_items; tile += gridDim.x, ++it) {
+        const uint32_t bn = (uint32_t)((tile < p.split_from) ? p.bn : (p.bn >> 1));
+        const uint32_t idesc = F16 ? make_idesc(ACC_F32, FMT_F16, FMT_F16, 0, B_NK ? 0 : 1, W8_BM, bn)
+                                   : make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, B_NK ? 0 : 1, W8_BM, bn);
         const int buf = it & 1;
         const uint32_t tphase = (it >> 1) & 1;
         if (!mbar_wait(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
@@ -238,9 +253,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     float* sb_s = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + Cfg::BAR_BYTES) + q * BN;
     uint8_t* my_stage = out_stage + q * 4096;  // [32 rows][128 B], 16-byte piece j of row r at (j ^ (r & 7))
     int it = 0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; tile < p.num_items; tile += gridDim.x, ++it) {
       const W8Tile t = w8_tile(p, tile);
-      const int n_blk = t.n_blk;
       const int buf = it & 1;
       const uint32_t tphase = (it >> 1) & 1;
       const int m = t.m0 + q * 32 + lane;
@@ -250,8 +264,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!F16 && p.C != nullptr) {
         const float* sbp = p.scale_b + (p.sb_mode == 2 ? (size_t)t.bB * p.N : 0);
         __syncwarp();  // the previous tile's reads of sb_s are done
-        for (int c = lane; c < p.bn; c += 32) {
-          const int n = n_blk * p.bn + c;
+        for (int c = lane; c < t.bn; c += 32) {
+          const int n = t.n0 + c;
           sb_s[c] = (p.sb_mode == 0) ? __ldg(sbp) : (n < p.N ? __ldg(sbp + n) : 0.f);
         }
         __syncwarp();
@@ -260,7 +274,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after_sync();
       const size_t row_off = ((size_t)t.bA * p.M + (row_ok ? m : 0)) * (size_t)p.N;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-      const int chunks = p.bn >> 5;
+      const int chunks = t.bn >> 5;
       // Whole row blocks go out as tiled bulk stores (coalesced, clipped at the tensor's edge); a partial
       // block of the grouped form must not touch the rows after it and uses per-row stores.
       const bool tma_out = p.tma_store != 0 && (p.meta == nullptr || t.rows == W8_BM);
@@ -278,7 +292,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (c >= chunks) break;
           tmem_ld_wait();                                                     // chunk c is in r[h]
           if (c + 1 < chunks) tmem_ld_32x32b_x32(taddr + (c + 1) * 32, r[h ^ 1]);  // chunk c + 1 in flight
-          const int n = n_blk * p.bn + c * 32;
+          const int n = t.n0 + c * 32;
           if (row_ok && n < p.N && p.acc_out != nullptr) {
             int4* dst = reinterpret_cast<int4*>(p.acc_out + row_off + n);
 #pragma unroll
@@ -346,11 +360,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         }
-        if (tma_out && n_blk * p.bn + c2 * 32 < p.N && t.m0 + q * 32 < p.M) {  // a box wholly outside is not issued
+        if (tma_out && t.n0 + c2 * 32 < p.N && t.m0 + q * 32 < p.M) {  // a box wholly outside is not issued
           fence_proxy_async_smem();  // this thread's staging writes are visible to the bulk-copy engine
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(&tmC, my_stage, n_blk * p.bn + c2 * 32, t.m0 + q * 32, t.bA);
+            tma_store_3d(&tmC, my_stage, t.n0 + c2 * 32, t.m0 + q * 32, t.bA);
             bulk_commit_group();
           }
         }
