@@ -31,7 +31,7 @@ constexpr int W4I8_W_COLS = W4_SLAB_K / 4;  // TMEM columns per slab of int8 wei
 
 template <int MT>
 struct W4I8Cfg {
-  static constexpr int RAW_STAGES = 8;
+  static constexpr int RAW_STAGES = 8;                 // even, like W_STAGES: a stage always belongs to one warp set
   static constexpr int A_STAGES = (MT <= 32) ? 8 : (MT == 64 ? 4 : 3);
   static constexpr int MMAW = (MT <= 32) ? 4 : (MT == 64 ? 2 : 1);
   static constexpr int W_STAGES = 4;
@@ -108,14 +108,14 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < RS; ++s) {
       mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], W4_DQ_WARPS);
+      mbar_init(&raw_empty[s], W4_DQ_WARPS / 2);  // the eight warps of the set that takes this slab
     }
     for (int s = 0; s < AS; ++s) {
       mbar_init(&a_full[s], 1);
       mbar_init(&a_empty[s], Cfg::MMAW);
     }
     for (int s = 0; s < WS; ++s) {
-      mbar_init(&w_full[s], W4_DQ_WARPS);
+      mbar_init(&w_full[s], W4_DQ_WARPS / 2);
       mbar_init(&w_empty[s], Cfg::MMAW);
     }
     for (int i = 0; i < 2; ++i) {
@@ -371,54 +371,58 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
   } else if (warp >= W4_FIRST_DQ_WARP && warp < W4_FIRST_XMMA_WARP) {
     // ----------------------------------------------------------------- unpack
-    // Warp (q, j): TMEM lanes 32q..32q+31, K sub-range [64j, 64j+64) of the slab = packed 16-byte chunks 2j and
-    // 2j+1 of the row = 64 int8 = 16 TMEM columns.  Word x holds nibbles n0..n7 of eight consecutive k:
-    // (x & 0x0f0f0f0f) = bytes (n0, n2, n4, n6), ((x >> 4) & 0x0f0f0f0f) = (n1, n3, n5, n7); the pre-pass stores
-    // the activations in that same order, so no byte shuffle is needed.  Two's-complement nibbles are biased
-    // by XOR 8 (value + 8 in 0..15) in the same lop3.
+    // Two sets of eight warps take alternate slabs, so that a warp's own chain of barrier round trips, shared
+    // memory loads and tensor-memory store (about 600 cycles) spans two slab periods instead of one: with
+    // every warp on every slab that chain, not the weight stream, set the pace.
+    // Warp (set, q, h): slabs with (index & 1) == set, TMEM lanes 32q..32q+31, K half h of the slab = packed
+    // 16-byte chunks 4h..4h+3 of the row = 128 int8 = 32 TMEM columns.  Word x holds nibbles n0..n7 of eight
+    // consecutive k: (x & 0x0f0f0f0f) = bytes (n0, n2, n4, n6), ((x >> 4) & 0x0f0f0f0f) = (n1, n3, n5, n7); the
+    // pre-pass stores the activations in that same order, so no byte shuffle is needed.  Two's-complement
+    // nibbles are biased by XOR 8 (value + 8 in 0..15) in the same lop3.
     const int wd = warp - W4_FIRST_DQ_WARP;
     const int q = warp & 3;
-    const int j = wd >> 2;
+    const int h = (wd >> 2) & 1;
+    const int set = wd >> 3;
     const int row = q * 32 + lane;
     const int sw = row & 7;
-    const uint32_t off0 = row * 128 + (((2 * j) ^ sw) << 4);
-    const uint32_t off1 = row * 128 + (((2 * j + 1) ^ sw) << 4);
-    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    int rs = 0, ws = 0;
-    uint32_t rphase = 0, wphase = 0;
-    bool ok = true;
-    while (ok && seg.next(tile, ks0, ks1)) {
-      for (int ks = ks0; ks < ks1; ++ks) {
-        if (!mbar_wait_warp(&raw_full[rs], rphase, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
-        const uint8_t* rawp = raw_base + rs * W4_RAW_PACKED;
-        const uint4 v0 = *reinterpret_cast<const uint4*>(rawp + off0);
-        const uint4 v1 = *reinterpret_cast<const uint4*>(rawp + off1);
-        const uint32_t x[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-        uint32_t o[16];
+    uint32_t off[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint32_t y = x[i] >> 4;
+    for (int c = 0; c < 4; ++c) off[c] = row * 128 + (((4 * h + c) ^ sw) << 4);
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const long long n_slabs = seg.end - seg.item;  // slabs of this CTA, in order
+    bool ok = true;
+    for (long long i = set; ok && i < n_slabs; i += 2) {
+      const int rs = (int)(i % RS), ws = (int)(i % WS);
+      const uint32_t rphase = (uint32_t)((i / RS) & 1), wphase = (uint32_t)((i / WS) & 1);
+      if (!mbar_wait_warp(&raw_full[rs], rphase, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
+      const uint8_t* rawp = raw_base + rs * W4_RAW_PACKED;
+      uint32_t o[32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(rawp + off[c]);
+        const uint32_t x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t y = x[e] >> 4;
           if (SIGNED) {
-            asm("lop3.b32 %0, %1, 0x0f0f0f0f, 0x08080808, 0x6a;" : "=r"(o[2 * i]) : "r"(x[i]));
-            asm("lop3.b32 %0, %1, 0x0f0f0f0f, 0x08080808, 0x6a;" : "=r"(o[2 * i + 1]) : "r"(y));
+            asm("lop3.b32 %0, %1, 0x0f0f0f0f, 0x08080808, 0x6a;" : "=r"(o[8 * c + 2 * e]) : "r"(x[e]));
+            asm("lop3.b32 %0, %1, 0x0f0f0f0f, 0x08080808, 0x6a;" : "=r"(o[8 * c + 2 * e + 1]) : "r"(y));
           } else {
-            o[2 * i] = x[i] & 0x0f0f0f0fu;
-            o[2 * i + 1] = y & 0x0f0f0f0fu;
+            o[8 * c + 2 * e] = x[e] & 0x0f0f0f0fu;
+            o[8 * c + 2 * e + 1] = y & 0x0f0f0f0fu;
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&raw_empty[rs]);
-        if (++rs == RS) { rs = 0; rphase ^= 1u; }
-
-        if (!mbar_wait_warp(&w_empty[ws], wphase ^ 1u, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
-        tc_fence_after_sync();
-        tmem_st_32x32b_x16(tmem_w + lane_addr + ws * W4I8_W_COLS + j * 16, o);
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&w_full[ws]);
-        if (++ws == WS) { ws = 0; wphase ^= 1u; }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&raw_empty[rs]);
+
+      if (!mbar_wait_warp(&w_empty[ws], wphase ^ 1u, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
+      tc_fence_after_sync();
+      tmem_st_32x32b_x32(tmem_w + lane_addr + ws * W4I8_W_COLS + h * 32, o);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&w_full[ws]);
     }
   }
 
