@@ -454,14 +454,23 @@ def run_reference(args):
 
 
 def run_case(args):
-    """A few eager launches of one configuration, for profilers: `--case cfg2|cfg3|cfg4|cfg5|act_quant [--m M] [--launches L]`.
+    """A few eager launches of one configuration, for profilers: `--case cfg2|cfg3|cfg4|cfg5|act_quant|w4a8 [--m M] [--launches L]`.
 
     Weight sets rotate so that reads stay L2-cold (cfg2: 20 sets = 160 MB; cfg5: 2 sets = 235 MB)."""
     import tilelang_ascend_b200 as q
     from oracle import qgemm_oracle as oc  # input generators only
     torch.cuda.set_device(0)
     n = args.launches
-    if args.case == "act_quant":  # --m rows (default 8192) of 8192 bf16 values
+    if args.case == "w4a8":  # fused W4A8 on the config-5 weight shape, --m tokens (default 16), two weight copies
+        Kq, Nq, Mq = 8192, 28672, args.m or 16
+        qBs = [torch.randint(0, 256, (Nq, Kq // 2), dtype=torch.uint8, device="cuda") for _ in range(2)]
+        A8 = torch.randint(-128, 128, (Mq, Kq), dtype=torch.int8, device="cuda")
+        wsq = torch.empty((Nq, Kq), dtype=torch.int8, device="cuda")
+        C = torch.empty((Mq, Nq), dtype=torch.int32, device="cuda")
+        kq = q.w4a8_gemm_cv(Mq, Nq, Kq)
+        for i in range(n):
+            kq(A8, qBs[i % 2], wsq, C)
+    elif args.case == "act_quant":  # --m rows (default 8192) of 8192 bf16 values
         X = torch.randn((args.m or 8192, 8192), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda()
         for _ in range(n):
             C, _s = q.act_quant(X)
@@ -496,7 +505,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-suite", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "act_quant"], default=None,
+    ap.add_argument("--case", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "act_quant", "w4a8"], default=None,
                     help="profiling helper: launch one configuration a few times and exit")
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--launches", type=int, default=4)

@@ -264,11 +264,12 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     for (int s = 0; s < AS; ++s) {
       mbar_init(&a_full[s], 1);
-      mbar_init(&a_empty[s], Cfg::MMAW);
+      // released by the one issuer that took the slab (round robin) or by all of them (K split)
+      mbar_init(&a_empty[s], ((WS % Cfg::MMAW) == 0 && (AS % Cfg::MMAW) == 0) ? 1 : Cfg::MMAW);
     }
     for (int s = 0; s < WS; ++s) {
       mbar_init(&w_full[s], W4_DQ_WARPS);
-      mbar_init(&w_empty[s], Cfg::MMAW);
+      mbar_init(&w_empty[s], ((WS % Cfg::MMAW) == 0 && (AS % Cfg::MMAW) == 0) ? 1 : Cfg::MMAW);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], Cfg::MMAW);
@@ -373,8 +374,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
   } else if (warp == 1 || warp >= W4_FIRST_XMMA_WARP) {
     // -------------------------------------------------------------- MMA issuers
-    // Issuer w of MMAW takes the K steps kk = w, w + MMAW, ... of every slab and accumulates them into its
-    // own accumulator (columns w*MT of the buffer).
+    // Each issuer accumulates into its own accumulator (columns w*MT of the buffer).  One issuing thread needs
+    // 900-1400 cycles per slab for its MMAs, the commits and the barrier round trips, more than the slab's HBM
+    // time, so the work is spread over MMAW threads, in one of two ways:
+    //  - round robin (ring depths that are multiples of MMAW, so that an issuer always meets the same stages
+    //    and every one of their phases, which its parity waits need): issuer w takes slab index % MMAW == w,
+    //    all of its K steps;
+    //  - K split (the 16- and 32-token tiles, whose rings are 3 / 9 and 2 / 6 deep): issuer w takes the K steps
+    //    kk = w, w + MMAW, ... of every slab.  Following every slab just to keep the parity waits safe made
+    //    round robin no faster there (measured), and those tiles are bound by the dequant warps anyway.
     const int mw = (warp == 1) ? 0 : (warp - W4_FIRST_XMMA_WARP + 1);
     if (mw < Cfg::MMAW && lane == 0) {
       constexpr uint32_t idesc = make_idesc(ACC_F32, FMT_F16, FMT_F16, 0, 0, W4_BN, MT);
@@ -382,7 +390,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const uint32_t a_base_u32 = smem_u32(a_base);
       int ws = 0, as = 0;
       uint32_t wphase = 0, aphase = 0;
+      // With ring depths that are multiples of MMAW an issuer always meets the same stages and every one of
+      // their phases; otherwise it has to follow the other issuers' slabs too (see below).
+      constexpr bool ROUND_ROBIN = (WS % Cfg::MMAW) == 0 && (AS % Cfg::MMAW) == 0;
       int it = 0;
+      int turn = 0;  // slab index % MMAW
       bool ok = true;
       while (ok && seg.next(tile, ks0, ks1)) {
         const int buf = it & 1;
@@ -392,20 +404,24 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         const uint32_t d = tmem_base + buf * (Cfg::MMAW * MT) + mw * MT;
         uint32_t started = 0;  // 0 for this issuer's first MMA of the segment: overwrite the accumulator
         for (int ks = ks0; ks < ks1; ++ks) {
-          if (!mbar_wait(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
-          if (!mbar_wait(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint64_t adesc0 = desc_hi | (uint64_t)(((a_base_u32 + as * Cfg::A_BYTES) & 0x3FFFFu) >> 4);
-          const uint32_t tW = tmem_w + ws * W4_W_COLS;
+          if (!ROUND_ROBIN || turn == mw) {
+            if (!mbar_wait(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+            if (!mbar_wait(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint64_t adesc0 = desc_hi | (uint64_t)(((a_base_u32 + as * Cfg::A_BYTES) & 0x3FFFFu) >> 4);
+            const uint32_t tW = tmem_w + ws * W4_W_COLS;
+            constexpr int STEPS = ROUND_ROBIN ? W4_SLAB_K / 16 : (W4_SLAB_K / 16) / Cfg::MMAW;
 #pragma unroll
-          for (int j = 0; j < (W4_SLAB_K / 16) / Cfg::MMAW; ++j) {  // 16 k per MMA: 8 TMEM columns, 32 bytes of smem
-            const int kk = j * Cfg::MMAW + mw;
-            const uint32_t off = (uint32_t)(((kk >> 2) * Cfg::A_KB_BYTES + (kk & 3) * 32) >> 4);
-            umma_f16_ts(d, tW + kk * 8, adesc0 + off, idesc, started);
-            started = 1u;
+            for (int j = 0; j < STEPS; ++j) {  // 16 k per MMA: 8 TMEM columns, 32 bytes of smem
+              const int kk = ROUND_ROBIN ? j : j * Cfg::MMAW + mw;
+              const uint32_t off = (uint32_t)(((kk >> 2) * Cfg::A_KB_BYTES + (kk & 3) * 32) >> 4);
+              umma_f16_ts(d, tW + kk * 8, adesc0 + off, idesc, started);
+              started = 1u;
+            }
+            umma_commit(&w_empty[ws]);
+            umma_commit(&a_empty[as]);
           }
-          umma_commit(&w_empty[ws]);
-          umma_commit(&a_empty[as]);
+          if (++turn == Cfg::MMAW) turn = 0;
           if (++ws == WS) { ws = 0; wphase ^= 1u; }
           if (++as == AS) { as = 0; aphase ^= 1u; }
         }
@@ -426,10 +442,15 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int q = warp & 3;
     const int nl = q * 32 + lane;  // weight row inside the tile == TMEM lane
     int it = 0;
+    constexpr bool ROUND_ROBIN_E = (WS % Cfg::MMAW) == 0 && (AS % Cfg::MMAW) == 0;  // as in the MMA issuers
+    long long first_slab = 0;  // CTA-local index of the segment's first slab: issuer (first_slab + i) % MMAW took slab i
     while (seg.next(tile, ks0, ks1)) {
       const int buf = it & 1;
       const uint32_t tphase = (it >> 1) & 1;
       ++it;
+      const int seg_len = ks1 - ks0;
+      const int first_turn = (int)(first_slab % Cfg::MMAW);
+      first_slab += seg_len;
       int b, n0, m0;
       w4_tile_coords(p, tile, MT, b, n0, m0);
       const int n = n0 + nl;
@@ -443,17 +464,19 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 #pragma unroll 1
         for (int c = 0; c < MT / CH; ++c) {
           uint32_t r[CH];
-          if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + c * CH, r);
-          else tmem_ld_32x32b_x32(taddr + c * CH, r);
-          tmem_ld_wait();
 #pragma unroll
-          for (int a = 1; a < Cfg::MMAW; ++a) {  // add the other issuers' accumulators, fixed order
-            uint32_t r2[CH];
-            if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + a * MT + c * CH, r2);
-            else tmem_ld_32x32b_x32(taddr + a * MT + c * CH, r2);
-            tmem_ld_wait();
+          for (int j = 0; j < CH; ++j) r[j] = 0u;  // +0.0f
 #pragma unroll
-            for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+          for (int a = 0; a < Cfg::MMAW; ++a) {  // add the issuers' accumulators in fixed order
+            // issuer a wrote its accumulator in this segment only if one of the segment's slabs was its turn
+            if (!ROUND_ROBIN_E || ((a - first_turn + Cfg::MMAW) % Cfg::MMAW) < seg_len) {
+              uint32_t r2[CH];
+              if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + a * MT + c * CH, r2);
+              else tmem_ld_32x32b_x32(taddr + a * MT + c * CH, r2);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+            }
           }
           if (full_tile) {
             if (n < p.N) {

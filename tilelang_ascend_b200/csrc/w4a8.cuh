@@ -26,7 +26,6 @@ struct W4A8Params {
   uint32_t* status;
   unsigned long long wait_limit_ns;
 };
-
 constexpr int W4I8_W_COLS = W4_SLAB_K / 4;  // TMEM columns per slab of int8 weights (4 per 32-bit column)
 
 template <int MT>
@@ -43,6 +42,9 @@ struct W4I8Cfg {
   static constexpr int SMEM_BYTES = RAW_STAGES * W4_RAW_PACKED + A_STAGES * A_BYTES + BAR_BYTES + 1024;
   static constexpr int CH = (MT < 32) ? 16 : 32;
   static_assert(ACC_COLS + W_STAGES * W4I8_W_COLS <= 512, "tensor memory budget");
+  // an MMA issuer takes every MMAW-th slab: with ring depths that are multiples of MMAW it always meets the same
+  // stages and every one of their phases, which is what makes its parity waits safe
+  static_assert(W_STAGES % MMAW == 0 && A_STAGES % MMAW == 0, "ring depths must be multiples of the issuer count");
 };
 
 // Pre-pass: int8 activations [M, K] -> the same values with every group of eight k reordered to
@@ -112,11 +114,11 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
     for (int s = 0; s < AS; ++s) {
       mbar_init(&a_full[s], 1);
-      mbar_init(&a_empty[s], Cfg::MMAW);
+      mbar_init(&a_empty[s], 1);  // released by the one issuer that took the slab
     }
     for (int s = 0; s < WS; ++s) {
       mbar_init(&w_full[s], W4_DQ_WARPS / 2);
-      mbar_init(&w_empty[s], Cfg::MMAW);
+      mbar_init(&w_empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], Cfg::MMAW);
@@ -213,8 +215,10 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
   } else if (warp == 1 || warp >= W4_FIRST_XMMA_WARP) {
     // -------------------------------------------------------------- MMA issuers
-    // Issuer w of MMAW takes the K steps kk = w, w + MMAW, ... of every slab and accumulates them into its
-    // own accumulator (columns w*MT of the buffer).
+    // Issuer w of MMAW takes every MMAW-th slab of this CTA (slab index % MMAW == w), all of its K steps, and
+    // accumulates into its own accumulator (columns w*MT of the buffer).  One issuing thread needs about 900
+    // cycles per slab for its MMAs, the commits and the barrier round trips, more than the slab's HBM time; with
+    // whole slabs dealt round-robin that cost is spread over MMAW threads.
     const int mw = (warp == 1) ? 0 : (warp - W4_FIRST_XMMA_WARP + 1);
     if (mw < Cfg::MMAW && lane == 0) {
       constexpr uint32_t idesc = make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, 0, W4_BN, MT);
@@ -223,6 +227,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       int ws = 0, as = 0;
       uint32_t wphase = 0, aphase = 0;
       int it = 0;
+      int turn = 0;  // slab index % MMAW
       bool ok = true;
       while (ok && seg.next(tile, ks0, ks1)) {
         const int buf = it & 1;
@@ -232,20 +237,22 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         const uint32_t d = tmem_base + buf * (Cfg::MMAW * MT) + mw * MT;
         uint32_t started = 0;  // 0 for this issuer's first MMA of the segment: overwrite the accumulator
         for (int ks = ks0; ks < ks1; ++ks) {
-          if (!mbar_wait(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
-          if (!mbar_wait(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint64_t adesc0 = desc_hi | (uint64_t)(((a_base_u32 + as * Cfg::A_BYTES) & 0x3FFFFu) >> 4);
-          const uint32_t tW = tmem_w + ws * W4I8_W_COLS;
+          if (turn == mw) {
+            if (!mbar_wait(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+            if (!mbar_wait(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint64_t adesc0 = desc_hi | (uint64_t)(((a_base_u32 + as * Cfg::A_BYTES) & 0x3FFFFu) >> 4);
+            const uint32_t tW = tmem_w + ws * W4I8_W_COLS;
 #pragma unroll
-          for (int j = 0; j < (W4_SLAB_K / 32) / Cfg::MMAW; ++j) {  // 32 k per MMA: 8 TMEM columns, 32 bytes of smem
-            const int kk = j * Cfg::MMAW + mw;
-            const uint32_t off = (uint32_t)(((kk >> 2) * Cfg::A_KB_BYTES + (kk & 3) * 32) >> 4);
-            umma_i8_ts(d, tW + kk * 8, adesc0 + off, idesc, started);
-            started = 1u;
+            for (int kk = 0; kk < W4_SLAB_K / 32; ++kk) {  // 32 k per MMA: 8 TMEM columns, 32 bytes of smem
+              const uint32_t off = (uint32_t)(((kk >> 2) * Cfg::A_KB_BYTES + (kk & 3) * 32) >> 4);
+              umma_i8_ts(d, tW + kk * 8, adesc0 + off, idesc, started);
+              started = 1u;
+            }
+            umma_commit(&w_empty[ws]);
+            umma_commit(&a_empty[as]);
           }
-          umma_commit(&w_empty[ws]);
-          umma_commit(&a_empty[as]);
+          if (++turn == Cfg::MMAW) turn = 0;
           if (++ws == WS) { ws = 0; wphase ^= 1u; }
           if (++as == AS) { as = 0; aphase ^= 1u; }
         }
@@ -268,11 +275,15 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const int q = warp & 3;
     const int nl = q * 32 + lane;  // weight row inside the tile == TMEM lane
     int it = 0;
+    long long first_slab = 0;  // CTA-local index of the segment's first slab: issuer (first_slab + i) % MMAW took slab i
     pdl_wait();  // row sums and zeroed counters come from the pre-pass kernel
     while (seg.next(tile, ks0, ks1)) {
       const int buf = it & 1;
       const uint32_t tphase = (it >> 1) & 1;
       ++it;
+      const int seg_len = ks1 - ks0;
+      const int first_turn = (int)(first_slab % Cfg::MMAW);
+      first_slab += seg_len;
       const int n = tile * W4_BN + nl;
       const bool full_tile = (ks0 == 0 && ks1 == p.KS);
       const int my_slot = (ks1 < p.KS) ? 2 * cta + 1 : 2 * cta;
@@ -283,17 +294,19 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < MT / CH; ++c) {
           uint32_t r[CH];
-          if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + c * CH, r);
-          else tmem_ld_32x32b_x32(taddr + c * CH, r);
-          tmem_ld_wait();
 #pragma unroll
-          for (int a = 1; a < Cfg::MMAW; ++a) {
-            uint32_t r2[CH];
-            if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + a * MT + c * CH, r2);
-            else tmem_ld_32x32b_x32(taddr + a * MT + c * CH, r2);
-            tmem_ld_wait();
+          for (int j = 0; j < CH; ++j) r[j] = 0u;
 #pragma unroll
-            for (int j = 0; j < CH; ++j) r[j] += r2[j];
+          for (int a = 0; a < Cfg::MMAW; ++a) {
+            // issuer a wrote its accumulator in this segment only if one of the segment's slabs was its turn
+            if (((a - first_turn + Cfg::MMAW) % Cfg::MMAW) < seg_len) {
+              uint32_t r2[CH];
+              if constexpr (CH == 16) tmem_ld_32x32b_x16(taddr + a * MT + c * CH, r2);
+              else tmem_ld_32x32b_x32(taddr + a * MT + c * CH, r2);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < CH; ++j) r[j] += r2[j];
+            }
           }
           if (full_tile) {
             if (n < p.N) {
