@@ -307,9 +307,11 @@ def dequant_gemm_fp16_wrapper(M: int, N: int, K: int, block_M: int, block_N: int
             raise ValueError(f"Buffer dtype mismatch for parameter A: expected {in_dt}, got {A.dtype}")
         on_cpu = not A.is_cuda
         if on_cpu:
+            # copies queue on the current stream without a host round trip each (pinned sources); the final
+            # .cpu() below waits for everything, so the sources may be reused as soon as the call returns
             dev = torch.device("cuda", torch.cuda.current_device())
-            A_, B_ = A.to(dev), B_packed.to(dev)
-            s_ = None if scales is None else scales.to(dev)
+            A_, B_ = A.to(dev, non_blocking=True), B_packed.to(dev, non_blocking=True)
+            s_ = None if scales is None else scales.to(dev, non_blocking=True)
         else:
             A_, B_, s_ = A, B_packed, scales
         C = w4a16_gemm(A_, B_, s_, zeros, group_size, out_dtype=out_dt)
