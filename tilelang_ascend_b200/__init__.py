@@ -13,6 +13,7 @@ from .ops import (  # noqa: F401
     dequant_gemm_fp16_wrapper,
     dequant_gemm_int8_wrapper,
     quant_matmul,
+    release_workspaces,
     simple_quant_batch_matmul,
     simple_quant_matmul,
     unpack_int4,

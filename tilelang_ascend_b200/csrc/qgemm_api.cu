@@ -324,7 +324,7 @@ static int w4a8_fused(const int8_t* A, const uint8_t* qB, int8_t* workspace, int
 
 extern "C" {
 
-int qgemm_version(void) { return 1000; }
+int qgemm_version(void) { return 1004; }  // 1.4: + grouped W8A8, activation quantiser, weight formats, fused W4A8
 
 const char* qgemm_last_error(void) { return g_err; }
 

@@ -201,6 +201,12 @@ _ZERO_MODES = {"original": 0, "rescale": 1, "quantized": 2}
 _WEIGHT_LAYOUTS = {"sequential": 0, "interleaved": 1}
 
 
+def release_workspaces():
+    """Drop the cached W4A16 scratch buffers (one per device and stream; from 1024 tokens on, or with a zeros
+    tensor, a buffer also holds the f16 copy of the weights, 2 * N * K bytes).  They are re-created on demand."""
+    _ws_cache.clear()
+
+
 def _w4a16_workspace(lib, batch, M, N, K, device, stream_handle, zeros_tensor=False):
     """Scratch buffer (split-K partial sums + arrival counters + prepared activations), one per
     (device, stream), grown on demand.
