@@ -277,7 +277,7 @@ def run_ours(args):
             line["cpu_baseline"] = cpu_base
         if suite is not None:
             line["suite"] = suite
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
@@ -452,7 +452,7 @@ def run_reference(args):
         "e2e": {"value": round(gbs, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def run_case(args):
@@ -499,6 +499,20 @@ def run_case(args):
     print(json.dumps({"case": args.case, "launches": n, "checksum": float(C.float().abs().mean())}))
 
 
+_RESULT_FD = None  # the process's original stdout, kept for the one JSON line
+
+
+def emit(line: dict):
+    """Write the result line to the original stdout (everything else this process and its libraries print goes to
+    stderr, see main())."""
+    text = json.dumps(line) + "\n"
+    if _RESULT_FD is None:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, text.encode())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -515,6 +529,12 @@ def main():
     args = ap.parse_args()
     if args.case is not None:
         return run_case(args)
+    # stdout carries exactly one JSON line: libraries that print there from native code (NCCL's version banner
+    # under torchrun) are sent to stderr for the rest of the run
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
