@@ -216,6 +216,7 @@ int qgemm_unpack_int4(const uint8_t* B_packed, int8_t* out, int64_t N, int64_t K
  * the reference wrapper casts to other types on the host afterwards, :263).  Requires K % 32 == 0
  * and N % 16 == 0.  Up to 128 tokens the weights are unpacked on their way to the tensor core and the workspace
  * only serves as scratch (its contents after the call are unspecified); above that it receives the int8 copy.
+ * Two calls that may overlap on the device must not share a workspace.
  */
 int qgemm_w4a8(const int8_t* A, const uint8_t* qB, int8_t* workspace, void* C, int64_t M, int64_t N, int64_t K,
                int signed_nibbles, int out_dtype, uint32_t* status, void* stream);

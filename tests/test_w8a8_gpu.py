@@ -209,3 +209,17 @@ def test_rejects_bad_arguments():
                        torch.zeros(24, 40, dtype=torch.int8, device="cuda"), torch.ones(40, device="cuda"))
     # the context is still usable after rejected calls
     assert torch.equal(k(A, A, s).cpu(), torch.zeros(64, 64, dtype=torch.float16))
+
+
+def test_empty_inputs_give_empty_outputs():
+    """No rows / no tokens: an empty result, no launch (the reference wrapper allocates the output with torch.empty)."""
+    q = _q()
+    B = torch.zeros(128, 64, dtype=torch.int8, device="cuda")
+    sb = torch.ones(64, device="cuda")
+    C = q.quant_matmul(torch.zeros(0, 128, dtype=torch.int8, device="cuda"), B, sb)
+    assert C.shape == (0, 64) and C.dtype == torch.float16
+    Cb = q.quant_matmul(torch.zeros(0, 5, 128, dtype=torch.int8, device="cuda"), torch.zeros(0, 128, 64, dtype=torch.int8, device="cuda"), sb)
+    assert Cb.shape == (0, 5, 64)
+    P = torch.zeros(64, 64, dtype=torch.uint8, device="cuda")
+    C4 = q.w4a16_gemm(torch.zeros(0, 128, dtype=torch.float16, device="cuda"), P, None)
+    assert C4.shape == (0, 64)

@@ -118,6 +118,8 @@ def quant_matmul(A, B, scale, scale_a=None, out_dtype=torch.float16, b_layout="K
     out_shape = ((batch,) if batched else ()) + (M, N)
     C = torch.empty(out_shape, dtype=out_dtype, device=dev)
     acc = torch.empty(out_shape, dtype=torch.int32, device=dev) if (return_accumulators and out_dtype != torch.int32) else None
+    if C.numel() == 0:  # no rows (or an empty batch): nothing to launch
+        return (C, acc) if acc is not None else C
     with torch.cuda.device(dev):
         rc = lib.qgemm_w8a8(A.data_ptr(), B.data_ptr(), _ptr(scale) if out_dtype != torch.int32 else None,
                             _ptr(scale_a) if out_dtype != torch.int32 else None, C.data_ptr(), _ptr(acc),
@@ -280,6 +282,8 @@ def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None
         zeros, group_size = 0, K
     sh = _stream_handle(stream, dev)
     C = torch.empty(lead + (M, N), dtype=out_dtype, device=dev)
+    if C.numel() == 0:  # no tokens: nothing to launch
+        return C
     with torch.cuda.device(dev):
         ws, need = _w4a16_workspace(lib, batch, M, N, K, dev, sh, zeros_t is not None)
         rc = lib.qgemm_w4a16_ex(A.data_ptr(), B_packed.data_ptr(), _ptr(scales), _ptr(zeros_t), int(zeros),
