@@ -20,7 +20,9 @@ import os
 
 import torch
 
-REFERENCE_ROOT = os.environ.get("QGEMM_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: QGEMM_REFERENCE_ROOT, else a directory "reference" beside this repository
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REFERENCE_ROOT = os.environ.get("QGEMM_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO), "reference"))
 
 
 def reference_available() -> bool:
