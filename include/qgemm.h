@@ -59,6 +59,13 @@ const char* qgemm_last_error(void);
 /* Per-wait limit of the kernels' bounded waits, in milliseconds (default 2000). */
 void qgemm_set_wait_limit_ms(uint32_t ms);
 
+/* Test hook, off by default (no counterpart in the reference).  While on, the W4A16 kernel for 9..32
+ * tokens leaves one accumulator hand-over of the launch unsignalled, so that one bounded wait of its
+ * epilogue runs out: the launch then ends after the wait limit with QGEMM_ST_TIMEOUT_EPILOGUE in `status`
+ * and an unspecified C, nothing is left in flight and the next call works normally.  It exists so that a
+ * test can see the time-out path end to end without faulting or hanging the device. */
+void qgemm_debug_withhold_commit(int on);
+
 /*
  * W8A8 quantized (batched) matmul.  Replaces the compiled `call` of
  * simple_quant_batch_matmul / simple_quant_matmul
@@ -104,9 +111,10 @@ int qgemm_w8a8_grouped(const int8_t* A, const int8_t* B, const float* scale_b, c
                        int b_layout, uint32_t* status, void* stream);
 
 /* Bytes of scratch memory qgemm_w4a16 needs for this problem on the current device (split-K partial
- * sums and arrival counters, the prepared activations and, from 1024 tokens on, the weights as f16: 2*N*K).  The first use of a scratch buffer must find its first
- * qgemm_w4a16_counter_bytes() bytes zeroed; the kernel leaves them zero.  Two launches that may
- * overlap on the device must not share a scratch buffer. */
+ * sums and arrival counters, the prepared activations and, from 1024 tokens on, the weights as f16: 2*N*K).
+ * The buffer needs no initialisation: every call zeroes the qgemm_w4a16_counter_bytes() bytes of arrival
+ * counters at its start, on the stream, and writes everything else before reading it.  Two launches
+ * that may overlap on the device must not share a scratch buffer. */
 int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int64_t qgemm_w4a16_counter_bytes(void);
 
@@ -118,6 +126,15 @@ int64_t qgemm_w4a16_counter_bytes(void);
  *   q[n,k]  = (B_packed[n, k/2] >> 4*(k%2)) & 0xF            (low nibble = even k)
  *   W[n,k]  = scales ? half(q - zero) * scales[k/group, n] : half(q)
  *   C[m,n]  = cast_out( sum_k float(A[m,k]) * float(W[n,k]) )   (fp32 accumulation)
+ *
+ * Where the scale enters depends on the token count.  Up to 32 tokens (groups of 128, multiples of 256 or
+ * the whole K) the kernels keep (q - zero) exact in f16, accumulate each group in fp32 and multiply the
+ * group's sum by its scale in fp32: C = cast_out( sum_g scales[g,n] * sum_{k in g} A[m,k] * (q - zero) ).
+ * Above that (and for groups of 32 / 64) every weight is scaled in f16 first, W rounded once as written
+ * above.  Both forms give the same result bit for bit when a row of A is one-hot, and differ otherwise by
+ * at most the rounding of that f16 product, 2^-11 relative per term; both meet rtol = atol = 1e-2 against
+ * the fp32 reference program.  The same inputs may therefore differ in the last bits between, say, M = 32
+ * and M = 33.
  *
  * A: [M, K] of a_dtype (F16 / BF16; bf16 is converted to f16 on the fly, as the reference wrapper does,
  *    example_dequant_gemm_fine_grained.py:211-214).  B_packed: [N, K/2] uint8.
@@ -188,8 +205,8 @@ int qgemm_w4a16_ex(const void* A, const uint8_t* B_packed, const void* scales, c
  * rejected with an error message (use qgemm_w4a16 then).  The function calls no cudaMalloc / cudaFree
  * and no allocating library routine.  The first call on each device looks up the array's device
  * address (one cudaGetSymbolAddress with that device current); make that first call outside any stream
- * capture.  All calls on a device share the one array: it keeps the previous call's contents (the
- * function re-zeroes the counters it needs on the given stream), and two calls that may overlap on the
+ * capture.  All calls on a device share the one array: it keeps the previous call's contents (every
+ * call re-zeroes the counters it needs on the given stream), and two calls that may overlap on the
  * GPU - different streams, or different host threads - race on it and must be serialised by the caller.
  */
 #define QGEMM_W4A16_NOALLOC_MAX_M 32

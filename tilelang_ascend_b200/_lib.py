@@ -13,7 +13,7 @@ import os
 import threading
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libqgemm.so")
+LIB_PATH = os.environ.get("QGEMM_LIB") or os.path.join(PKG, "libqgemm.so")  # QGEMM_LIB: another build of the library
 
 DT_F16, DT_BF16, DT_I32 = 0, 1, 2
 B_KN, B_NK = 0, 1
@@ -28,6 +28,7 @@ SIGNATURES = {
     "qgemm_init": (_c.c_int, []),
     "qgemm_last_error": (_c.c_char_p, []),
     "qgemm_set_wait_limit_ms": (None, [_c.c_uint32]),
+    "qgemm_debug_withhold_commit": (None, [_c.c_int]),
     "qgemm_w8a8": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                               _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
                               _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
@@ -71,7 +72,7 @@ def load() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        if os.environ.get("QGEMM_NO_BUILD") != "1":
+        if os.environ.get("QGEMM_NO_BUILD") != "1" and not os.environ.get("QGEMM_LIB"):
             try:
                 from . import build as _build
                 if _build.needs_build():

@@ -10,6 +10,7 @@
 
 #include "w4a16.cuh"
 #include "w4a16_decode.cuh"
+#include "w4a16_gs.cuh"
 #include "act_quant.cuh"
 #include "w4a8.cuh"
 #include "w8a8.cuh"
@@ -93,6 +94,14 @@ int set_smem_w4() {
   return 0;
 }
 
+template <int MT>
+int set_smem_w4g() {
+  using C = qg::W4GCfg<MT>;
+  if (set_smem(qg::w4a16_gs_kernel<MT, false>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_gs_kernel<MT, true>, C::SMEM_BYTES)) return -1;
+  return 0;
+}
+
 // Once per device, with that device current.
 int ensure_device(int* sm_count) {
   int dev = 0;
@@ -113,6 +122,7 @@ int ensure_device(int* sm_count) {
     }
     if (set_smem_w8<128>() || set_smem_w8<256>() || set_smem_w8_pair()) return -1;
     if (set_smem_w4<16>() || set_smem_w4<32>() || set_smem_w4<64>() || set_smem_w4<128>()) return -1;
+    if (set_smem_w4g<16>() || set_smem_w4g<32>()) return -1;
     if (set_smem_w4i8<16>() || set_smem_w4i8<32>() || set_smem_w4i8<64>() || set_smem_w4i8<128>()) return -1;
     if (set_smem_w4d<0>() || set_smem_w4d<1>() || set_smem_w4d<2>() || set_smem_w4d<4>()) return -1;
     st.sm_count = prop.multiProcessorCount;
@@ -184,6 +194,29 @@ int launch_w4(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUt
   return launch_pdl(qg::w4a16_gemm_kernel<MT, false>, grid, qg::W4_THREADS, qg::W4Cfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p);
 }
 
+// Test hook (qgemm_debug_withhold_commit): see W4GDebug.
+int g_w4g_withhold_commit = 0;
+
+template <int MT>
+int launch_w4g(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA, const qg::W4A16Params& p,
+               int grid, cudaStream_t s) {
+  qg::W4GDebug dbg;
+  dbg.withhold_last_commit = g_w4g_withhold_commit;
+  if (bf) return launch_pdl(qg::w4a16_gs_kernel<MT, true>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
+  return launch_pdl(qg::w4a16_gs_kernel<MT, false>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
+}
+
+// The group-sum kernel (w4a16_gs.cuh) serves token tiles of 16 and 32 when the scale groups are 128 wide, a
+// multiple of 256 or the whole K (or there are no scales).  QGEMM_W4_GS=0 disables it; QGEMM_W4_GS_MIN_M moves
+// the boundary to the register-operand decode kernel (default: the decode kernel keeps M <= 8).
+bool w4_use_gs(int64_t M, int mt, bool has_scales, int64_t group, int64_t K) {
+  static const int enabled = getenv("QGEMM_W4_GS") ? atoi(getenv("QGEMM_W4_GS")) : 1;
+  static const int min_m = getenv("QGEMM_W4_GS_MIN_M") ? atoi(getenv("QGEMM_W4_GS_MIN_M")) : -1;
+  if (!enabled || M > 32) return false;
+  if (min_m >= 0 ? M < min_m : mt < 16) return false;
+  return !has_scales || group == 128 || group % 256 == 0 || group >= K;
+}
+
 template <int FLUSH, int NB>
 int launch_w4d_nb(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
                   const qg::W4A16Params& p, int grid, cudaStream_t s) {
@@ -208,8 +241,13 @@ int w4_decode_max_m() {
 }
 bool w4_use_decode(int64_t M) { return M <= w4_decode_max_m(); }
 // Token-tile height: 8 for the decode kernel, 16..128 for the tcgen05 kernel.
+int w4_gs_min_m() {
+  static const int v = getenv("QGEMM_W4_GS_MIN_M") ? atoi(getenv("QGEMM_W4_GS_MIN_M")) : -1;
+  return v;
+}
 int w4_pick_mt(int64_t M) {
-  if (w4_use_decode(M)) return M <= 8 ? 8 : 16;
+  const bool gs_takes_it = w4_gs_min_m() >= 0 && M >= w4_gs_min_m() && M <= 32;
+  if (w4_use_decode(M) && !gs_takes_it) return M <= 8 ? 8 : 16;
   return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
 }
 
@@ -329,6 +367,8 @@ int qgemm_version(void) { return 1004; }  // 1.4: + grouped W8A8, activation qua
 const char* qgemm_last_error(void) { return g_err; }
 
 void qgemm_set_wait_limit_ms(uint32_t ms) { g_wait_limit_ns = (unsigned long long)ms * 1000000ull; }
+
+void qgemm_debug_withhold_commit(int on) { g_w4g_withhold_commit = on ? 1 : 0; }
 
 int qgemm_init(void) {
   int sms = 0;
@@ -657,9 +697,11 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     const uint32_t box[3] = {128, 128, 1};
     if (encode_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B_packed, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
   }
+  // the group-sum kernel fetches the scale rows of a slab's two 128-k halves: two rows for groups of 128, else one
+  const bool use_gs = !dequant_once && mt >= 16 && w4_use_gs(M, mt, scales != nullptr, group, K);
   int scale_rows = 1;
   if (scales != nullptr) {
-    scale_rows = group < 256 ? (int)(256 / group) : 1;
+    scale_rows = use_gs ? (group == 128 ? 2 : 1) : (group < 256 ? (int)(256 / group) : 1);
     const uint64_t dims[3] = {(uint64_t)N, (uint64_t)(K / group), (uint64_t)batch};
     const uint64_t str[2] = {(uint64_t)N * 2, (uint64_t)(K / group) * (uint64_t)N * 2};
     const uint32_t box[3] = {128, (uint32_t)scale_rows, 1};
@@ -706,7 +748,8 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     qg::w4a16_prepare_activations<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint4*>(A),
                                                                   reinterpret_cast<uint4*>(a_prepared), n_chunks,
                                                                   a_dtype == QGEMM_DT_BF16 ? 1 : 0,
-                                                                  weight_format == QGEMM_W4_SEQUENTIAL ? 1 : 0);
+                                                                  weight_format == QGEMM_W4_SEQUENTIAL ? 1 : 0,
+                                                                  p.ws_counters, (int)(kW4CounterBytes / 4));
     CUDA_OK(cudaGetLastError());
   }
   if (dequant_once) {
@@ -723,7 +766,11 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     CUDA_OK(cudaGetLastError());
     return w4_f16_gemm(a_prepared, w16, C, batch, M, N, K, bf, status, s, sms);
   }
-  if (w4_use_decode(M)) {
+  if (use_gs) {
+    if (mt == 16) return launch_w4g<16>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    return launch_w4g<32>(bf, tmW, tmS, tmA, p, (int)grid, s);
+  }
+  if (w4_use_decode(M) && mt <= 16 && M <= w4_decode_max_m()) {
     if (scales == nullptr) return launch_w4d<0>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);
     if (group >= 128) return launch_w4d<4>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);
     if (group == 64) return launch_w4d<2>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);
@@ -865,9 +912,9 @@ extern "C" int qgemm_w4a16_noalloc(const void* A, const uint8_t* B_packed, const
                 (long long)need, (long long)kStaticScratchBytes);
   void* scratch = nullptr;
   if (static_scratch_for_current_device(&scratch)) return -1;
-  // The array keeps whatever the previous call left behind.  The arrival counters must start at zero;
-  // everything else is written before it is read.
-  CUDA_OK(cudaMemsetAsync(scratch, 0, (size_t)kW4CounterBytes, static_cast<cudaStream_t>(stream)));
+  // The array keeps whatever the previous call left behind.  The arrival counters must start at zero: the
+  // pre-pass kernel of every call zeroes them; everything else is written before it is read.  Nothing is put
+  // on the stream before qgemm_w4a16 has validated the remaining arguments.
   return qgemm_w4a16(A, B_packed, scales, zero, group, C, scratch, kStaticScratchBytes, M, N, K, a_dtype, out_dtype,
                      status, stream);
 }

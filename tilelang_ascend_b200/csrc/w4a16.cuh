@@ -33,7 +33,7 @@ namespace qg {
 struct W4A16Params {
   void* C;               // [M, N] f16 / bf16
   float* ws_partials;    // scratch: 2 * grid slots of [MT][128] fp32
-  uint32_t* ws_counters; // scratch: grid counters, zero on entry, left zero on exit
+  uint32_t* ws_counters; // scratch: grid counters, zeroed by the pre-pass kernel of every call
   int M, N, K;
   int group;            // quantisation group size along K
   int zero;             // integer zero point (0..15)
@@ -207,11 +207,14 @@ w4a16_dequant_weights(const uint4* __restrict__ packed, const __half* __restrict
 }
 
 // Pre-pass: activations [M, K] (f16 or bf16) -> f16 with every group of eight K values reordered to
-// 0,4,1,5,2,6,3,7.  One 16-byte chunk per thread.
+// 0,4,1,5,2,6,3,7.  One 16-byte chunk per thread.  Block 0 also zeroes the split-K arrival counters, so
+// every call starts from clean counters whatever an earlier (possibly aborted) call left in the scratch.
 __global__ void __launch_bounds__(256)
 w4a16_prepare_activations(const uint4* __restrict__ in, uint4* __restrict__ out, long long n_chunks, int is_bf16,
-                          int permute) {
+                          int permute, uint32_t* __restrict__ counters, int n_counters) {
   pdl_launch_dependents();  // the GEMM kernel behind may set up and start streaming weights meanwhile
+  if (blockIdx.x == 0)
+    for (int c = threadIdx.x; c < n_counters; c += blockDim.x) counters[c] = 0u;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_chunks) return;
   uint4 v = in[i];
@@ -441,6 +444,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     constexpr int CH = Cfg::CH;
     const int q = warp & 3;
     const int nl = q * 32 + lane;  // weight row inside the tile == TMEM lane
+    pdl_wait();  // the arrival counters are zeroed by the pre-pass kernel in front of this one
     int it = 0;
     constexpr bool ROUND_ROBIN_E = (WS % Cfg::MMAW) == 0 && (AS % Cfg::MMAW) == 0;  // as in the MMA issuers
     long long first_slab = 0;  // CTA-local index of the segment's first slab: issuer (first_slab + i) % MMAW took slab i

@@ -179,6 +179,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   if (warp == W4D_FIN_WARP) {
     // ---------------------------------------------------------------- finisher
     // Lane l owns the float4 column group l of every token row of the tile.
+    pdl_wait();  // the arrival counters are zeroed by the pre-pass kernel in front of this one
     int it = 0;
     while (seg.next(tile, ks0, ks1)) {
       const int buf = it & 1;
