@@ -206,14 +206,18 @@ int launch_w4g(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CU
   return launch_pdl(qg::w4a16_gs_kernel<MT, false>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
 }
 
-// The group-sum kernel (w4a16_gs.cuh) serves token tiles of 16 and 32 when the scale groups are 128 wide, a
-// multiple of 256 or the whole K (or there are no scales).  QGEMM_W4_GS=0 disables it; QGEMM_W4_GS_MIN_M moves
-// the boundary to the register-operand decode kernel (default: the decode kernel keeps M <= 8).
-bool w4_use_gs(int64_t M, int mt, bool has_scales, int64_t group, int64_t K) {
+// The group-sum kernel (w4a16_gs.cuh) serves up to 32 tokens when the scale groups are 128 wide, a multiple of
+// 256 or the whole K (or there are no scales); it is faster than the register-operand decode kernel at every
+// token count (K=8192, N=28672: 36 against 40 us at one token, 37 against 42 us at eight).  Groups of 32 / 64 keep
+// the decode kernel (M <= 8) and the per-weight-scale tcgen05 kernel.  QGEMM_W4_GS=0 disables the group-sum kernel,
+// QGEMM_W4_GS_MIN_M raises the token count from which it is used.
+int w4_gs_min_m() {
+  static const int v = getenv("QGEMM_W4_GS_MIN_M") ? atoi(getenv("QGEMM_W4_GS_MIN_M")) : 1;
+  return v;
+}
+bool w4_gs_shape_ok(int64_t M, bool has_scales, int64_t group, int64_t K) {
   static const int enabled = getenv("QGEMM_W4_GS") ? atoi(getenv("QGEMM_W4_GS")) : 1;
-  static const int min_m = getenv("QGEMM_W4_GS_MIN_M") ? atoi(getenv("QGEMM_W4_GS_MIN_M")) : -1;
-  if (!enabled || M > 32) return false;
-  if (min_m >= 0 ? M < min_m : mt < 16) return false;
+  if (!enabled || M > 32 || M < w4_gs_min_m()) return false;
   return !has_scales || group == 128 || group % 256 == 0 || group >= K;
 }
 
@@ -241,13 +245,10 @@ int w4_decode_max_m() {
 }
 bool w4_use_decode(int64_t M) { return M <= w4_decode_max_m(); }
 // Token-tile height: 8 for the decode kernel, 16..128 for the tcgen05 kernel.
-int w4_gs_min_m() {
-  static const int v = getenv("QGEMM_W4_GS_MIN_M") ? atoi(getenv("QGEMM_W4_GS_MIN_M")) : -1;
-  return v;
-}
-int w4_pick_mt(int64_t M) {
-  const bool gs_takes_it = w4_gs_min_m() >= 0 && M >= w4_gs_min_m() && M <= 32;
-  if (w4_use_decode(M) && !gs_takes_it) return M <= 8 ? 8 : 16;
+// Token-tile height: 16 / 32 for the group-sum kernel, 8 for the decode kernel, 16..128 for the tcgen05 kernel.
+int w4_pick_mt(int64_t M, bool gs) {
+  if (gs) return M <= 16 ? 16 : 32;
+  if (w4_use_decode(M)) return M <= 8 ? 8 : 16;
   return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
 }
 
@@ -544,7 +545,8 @@ static int64_t w4_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K
   int sms = 0;
   if (ensure_device(&sms)) return -1;
   const int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
-  const int mt = w4_pick_mt(M);
+  // sized for whichever small-token kernel the scale groups will select (the group-sum kernel's tile is the taller)
+  const int mt = M <= 32 ? w4_pick_mt(M, true) : w4_pick_mt(M, false);
   // the arrival counters first (fixed place whatever the tile height), then two partial slots of
   // [MT][128] fp32 per CTA, then the f16 copy of the activations in the kernel's K order
   // ... and, for the large-token path, the dequantised f16 weights
@@ -687,7 +689,8 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
 
   int sms = 0;
   if (ensure_device(&sms)) return -1;
-  const int mt = w4_pick_mt(M);
+  const bool use_gs = !dequant_once && w4_gs_shape_ok(M, scales != nullptr, group, K);
+  const int mt = w4_pick_mt(M, use_gs);
 
   CUtensorMap tmW, tmS, tmA;
   memset(&tmS, 0, sizeof(tmS));
@@ -698,7 +701,6 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     if (encode_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B_packed, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
   }
   // the group-sum kernel fetches the scale rows of a slab's two 128-k halves: two rows for groups of 128, else one
-  const bool use_gs = !dequant_once && mt >= 16 && w4_use_gs(M, mt, scales != nullptr, group, K);
   int scale_rows = 1;
   if (scales != nullptr) {
     scale_rows = use_gs ? (group == 128 ? 2 : 1) : (group < 256 ? (int)(256 / group) : 1);
@@ -739,6 +741,18 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
   p.wait_limit_ns = g_wait_limit_ns;
   int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
   if (p.total_items < grid) grid = p.total_items;
+  // Small problems (a few slabs per CTA): prefer a slightly smaller grid that cuts every tile into equal K ranges,
+  // one per CTA, over an even deal that leaves most CTAs with two partial tiles and so two split-K hand-overs.
+  if (p.total_items <= 8 * grid && p.total_items > grid) {
+    for (int64_t g2 = grid; g2 * 4 >= grid * 3; --g2) {
+      if (p.total_items % g2 != 0) continue;
+      const int64_t per = p.total_items / g2;
+      if (p.KS % per == 0) {
+        grid = g2;
+        break;
+      }
+    }
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf = out_dtype == QGEMM_DT_BF16;
   {
