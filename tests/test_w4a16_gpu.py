@@ -284,3 +284,90 @@ def test_config5_prefill_m4096_band_and_linearity():
     _close(C[:, cols.cuda()], ref)
     C2 = q.w4a16_gemm(Ad * 2, Pd, Sd, 8, 128)
     torch.testing.assert_close(C2.float(), C.float() * 2, rtol=1e-2, atol=1e-2)
+
+
+def _cfg5_column_sum_of_weights(packed, scales, zero=8, group=128):
+    """sum over n of the dequantised weights W[n, k] = half(q - zero) * s[k / g, n], in float64, group by group."""
+    N, K = packed.shape[0], packed.shape[1] * 2
+    q = oc.unpack_uint4(packed).to(torch.float32)  # [N, K]
+    wsum = torch.empty(K, dtype=torch.float64)
+    for g in range(K // group):
+        w = ((q[:, g * group:(g + 1) * group] - zero).half() * scales[g, :, None]).double()  # one f16 rounding, as the operator's contract says
+        wsum[g * group:(g + 1) * group] = w.sum(dim=0)
+    return wsum
+
+
+@pytest.fixture(scope="module")
+def cfg5_weights():
+    _, packed, scales = oc.make_config_inputs("cfg5", M=1)
+    return packed, scales, _cfg5_column_sum_of_weights(packed, scales), packed.cuda(), scales.cuda()
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 64, 512, 4096])
+def test_config5_whole_output_identity(cfg5_weights, M):
+    """An identity every output tile takes part in, at full size: sum_n C[m, n] == A[m, :] . sum_n W[n, :].
+    A tile written to the wrong place, left out or added twice (a lost or duplicated split-K hand-over) moves a
+    row sum by about sqrt(128) * |C|, far outside the bar, which is the rounding of 28672 bf16 outputs."""
+    q = _q()
+    packed, scales, wsum, Pd, Sd = cfg5_weights
+    A, _, _ = oc.make_config_inputs("cfg5", M=M)
+    C = q.w4a16_gemm(A.cuda(), Pd, Sd, 8, 128)
+    got = C.double().sum(dim=1).cpu()
+    want = A.half().double() @ wsum  # the operator converts bf16 activations to f16 first, as the reference wrapper does
+    N = packed.shape[0]
+    cmax = C.float().abs().max().item()
+    bar = 6.0 * (N ** 0.5) * cmax * 2.0 ** -9 + 1e-3 * want.abs().max().item()
+    assert (got - want).abs().max().item() <= bar, ((got - want).abs().max().item(), bar)
+    assert torch.isfinite(C.float()).all()
+
+
+def test_kernels_on_either_side_of_a_switch_agree():
+    """Up to 32 tokens the group scale multiplies the group's fp32 sum, above that every weight is scaled in f16
+    first: the same token row through both kernels differs by at most that f16 product's rounding, 2^-11
+    relative per term - far inside the operator's tolerance, and the bar here."""
+    q = _q()
+    M, K, N = 33, 2048, 512
+    A, packed, scales = oc.make_w4a16_inputs(M, K, N, "float16", 128, seed=11)
+    Ad, Pd, Sd = A.cuda(), packed.cuda(), scales.cuda()
+    C33 = q.w4a16_gemm(Ad, Pd, Sd, 8, 128)                      # per-weight scale (tcgen05 kernel)
+    C32 = q.w4a16_gemm(Ad[:32].contiguous(), Pd, Sd, 8, 128)    # group-sum kernel
+    C8 = q.w4a16_gemm(Ad[:8].contiguous(), Pd, Sd, 8, 128)
+    ref = oc.dequant_gemm_fp16_ref(A, packed, "float16", scales, 8, 128)
+    _close(C33, ref)
+    _close(C32, ref[:32])
+    assert torch.equal(C8, C32[:8])  # same kernel, same arithmetic per row whatever the token count
+    # |sum_k a w (1 + e_k)| with |e_k| <= 2^-11: bounded by 2^-11 * sum |a w|, plus the output's own rounding
+    W = oc.dequant_weight_ref(packed, scales, 8, 128).float()
+    bound = (A.float().abs() @ W.abs().t()) * 2.0 ** -11 + ref.float().abs() * 2.0 ** -9 + 1e-3
+    assert ((C33[:32].float() - C32.float()).abs().cpu() <= bound[:32]).all()
+
+
+def test_bounded_wait_expires_cleanly_and_the_next_call_is_exact():
+    """The time-out path end to end, without faulting or hanging anything: with the test hook on, one
+    accumulator hand-over of the launch is never signalled, so one wait of the epilogue runs into its limit
+    (20 ms here).  The kernel must return by itself with QGEMM_ST_TIMEOUT_EPILOGUE in the status word, and the
+    next ordinary call on the same device must be correct."""
+    q = _q()
+    from tilelang_ascend_b200 import _lib
+    lib = _lib.load()
+    A, packed, scales = oc.make_w4a16_inputs(16, 1024, 256, "float16", 128, seed=5)
+    Ad, Pd, Sd = A.cuda(), packed.cuda(), scales.cuda()
+    ref = oc.dequant_gemm_fp16_ref(A, packed, "float16", scales, 8, 128)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    try:
+        lib.qgemm_set_wait_limit_ms(20)
+        lib.qgemm_debug_withhold_commit(1)
+        q.w4a16_gemm(Ad, Pd, Sd, 8, 128, status=status)
+        torch.cuda.synchronize()  # returns: the kernel gave up by itself
+        assert int(status.item()) == 3  # QGEMM_ST_TIMEOUT_EPILOGUE
+        with pytest.raises(q.QGemmError, match="bounded wait ran out"):
+            q.w4a16_gemm(Ad, Pd, Sd, 8, 128, check_status=True)
+    finally:
+        lib.qgemm_debug_withhold_commit(0)
+        lib.qgemm_set_wait_limit_ms(2000)
+    status.zero_()
+    C = q.w4a16_gemm(Ad, Pd, Sd, 8, 128, status=status)
+    _close(C, ref)
+    assert int(status.item()) == 0
+    C2 = q.w4a16_gemm(Ad, Pd, Sd, 8, 128, check_status=True)
+    assert torch.equal(C, C2)

@@ -50,6 +50,14 @@ def test_noalloc_rejects_sizes_beyond_its_scratch():
     A, P, S = [t.cuda() for t in oc.make_w4a16_inputs(33, 256, 128, "float16", 128, seed=1)]
     rc, _ = _call_noalloc(lib, A, P, S, 8, 128, torch.float16)
     assert rc != 0 and "M <= 32" in _lib.last_error()
+    # K beyond the built-in array's activation area
+    A, P, S = [t.cuda() for t in oc.make_w4a16_inputs(1, 16384 + 128, 8, "float16", 128, seed=3)]
+    rc, _ = _call_noalloc(lib, A, P, S, 8, 128, torch.float16)
+    assert rc != 0 and "K <= 16384" in _lib.last_error()
+    # arguments the ordinary entry point rejects are rejected here too, before anything is put on the stream
+    A, P, S = [t.cuda() for t in oc.make_w4a16_inputs(4, 256, 128, "float16", 128, seed=4)]
+    rc, _ = _call_noalloc(lib, A, P, S, 8, 48, torch.float16)
+    assert rc != 0 and "group" in _lib.last_error()
     # still usable afterwards
     A, P, S = [t.cuda() for t in oc.make_w4a16_inputs(8, 256, 128, "float16", 128, seed=2)]
     rc, got = _call_noalloc(lib, A, P, S, 8, 128, torch.float16)

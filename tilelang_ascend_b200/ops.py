@@ -196,38 +196,34 @@ def simple_quant_matmul(M: int, N: int, K: int, scale_size, block_M: int, block_
 
 
 # ------------------------------------------------------------------------------------------ W4A16
-_ws_cache = {}
-
-
 _ZERO_MODES = {"original": 0, "rescale": 1, "quantized": 2}
 _WEIGHT_LAYOUTS = {"sequential": 0, "interleaved": 1}
 
 
 def release_workspaces():
-    """Drop the cached W4A16 scratch buffers (one per device and stream; from 1024 tokens on, or with a zeros
-    tensor, a buffer also holds the f16 copy of the weights, 2 * N * K bytes).  They are re-created on demand."""
-    _ws_cache.clear()
+    """Kept for callers of earlier versions: scratch buffers are allocated per call now (as the reference wrapper
+    allocates its workspaces, tilelang/jit/adapter/cython/cython_wrapper.pyx:102-141), so there is nothing to drop."""
 
 
 def _w4a16_workspace(lib, batch, M, N, K, device, stream_handle, zeros_tensor=False):
-    """Scratch buffer (split-K partial sums + arrival counters + prepared activations), one per
-    (device, stream), grown on demand.
+    """Scratch buffer of one call (split-K partial sums + arrival counters + prepared activations, and from 1024
+    tokens on, or with a zeros tensor, the f16 copy of the weights).
 
-    The counters must start at zero and the kernel leaves them zero, so the buffer is zeroed once, at
-    creation.  Launches on different streams get different buffers because they may overlap on the GPU."""
+    It needs no initialisation: the call zeroes its arrival counters itself, on its stream.  It is allocated per
+    call from torch's caching allocator, so no launch ever sees a buffer that another call may still be using or
+    that a captured CUDA graph still points to; when the launch stream is not torch's current stream the buffer
+    is tied to that stream so that the allocator does not hand it out again too early."""
     need = lib.qgemm_w4a16_ex_workspace_bytes(batch, M, N, K, 1 if zeros_tensor else 0)
     if need < 0:
         raise _lib.QGemmError("qgemm_w4a16_ex_workspace_bytes: " + _lib.last_error())
-    key = (device.index, stream_handle)
-    ws = _ws_cache.get(key)
-    if ws is None or ws.numel() < need:
-        ws = torch.zeros(need, dtype=torch.uint8, device=device)
-        _ws_cache[key] = ws
+    ws = torch.empty(need, dtype=torch.uint8, device=device)
+    if stream_handle != torch.cuda.current_stream(device).cuda_stream:
+        ws.record_stream(torch.cuda.ExternalStream(stream_handle, device=device))
     return ws, need
 
 
 def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None, stream=None, status=None,
-               zeros_mode="original", weight_layout="sequential"):
+               zeros_mode="original", weight_layout="sequential", check_status=False):
     """``C[M,N] = A[M,K] @ W[N,K].T`` with ``W = (unpack_u4(B_packed) - zeros).half() * scales[k // g, n]``
     (or the raw nibble values when ``scales is None``).  CUDA tensors in, CUDA tensor out.
 
@@ -238,7 +234,11 @@ def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None
 
     Batched form: ``A[Batch,M,K]``, ``B_packed[Batch,N,K/2]``, ``scales[Batch,K/g,N]`` -> ``C[Batch,M,N]``,
     independent problems of one shape in a single launch (the batch dimension of ``simple_quant_batch_matmul``
-    carried over to the W4A16 operator)."""
+    carried over to the W4A16 operator).
+
+    ``status``: optional int32 CUDA tensor of one element that receives a non-zero code if a bounded wait inside
+    the kernel ran out (the result is then unspecified).  ``check_status=True`` allocates that word, waits for the
+    launch to finish and raises ``QGemmError`` if it is non-zero - a synchronising debug aid, off by default."""
     lib = _lib.load()
     _require_cuda(A, "A")
     dev = A.device
@@ -284,6 +284,8 @@ def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None
     C = torch.empty(lead + (M, N), dtype=out_dtype, device=dev)
     if C.numel() == 0:  # no tokens: nothing to launch
         return C
+    if check_status and status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         ws, need = _w4a16_workspace(lib, batch, M, N, K, dev, sh, zeros_t is not None)
         rc = lib.qgemm_w4a16_ex(A.data_ptr(), B_packed.data_ptr(), _ptr(scales), _ptr(zeros_t), int(zeros),
@@ -291,6 +293,12 @@ def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None
                                 C.data_ptr(), ws.data_ptr(), need, batch, M, N, K, _ABI_DT[A.dtype],
                                 _ABI_DT[out_dtype], _ptr(status), sh)
     _lib.check(rc, "qgemm_w4a16")
+    if check_status:
+        torch.cuda.synchronize(dev)  # the launch may be on any stream
+        code = int(status.item())
+        if code != 0:
+            raise _lib.QGemmError(f"qgemm_w4a16: a bounded wait ran out on the device ({_lib.STATUS_NAMES.get(code, code)}); "
+                                  "the result is unspecified")
     return C
 
 
