@@ -190,6 +190,40 @@ int qgemm_w4a16_ex(const void* A, const uint8_t* B_packed, const void* scales, c
                    void* stream);
 
 /*
+ * Gathered W4A16 for weights whose output features are split over several GPUs of one node (one process per
+ * GPU): this rank computes its [M, N] block and writes it straight into columns [col0, col0 + N) of n_dst
+ * row-major [M, ldc] buffers - its own and every peer's, the peers' mapped into this process with
+ * qgemm_ipc_open - with ordinary stores from the kernel's epilogue, so the output crosses NVLink while the
+ * rest of the GEMM still runs and no collective has to move or re-arrange it afterwards.  The one-sided
+ * counterpart in the reference is the put of src/tl_templates/ascend/common.h:358-408 as used by
+ * examples/shmem/shmem_mm_test_put_nbi.py:69-74; there is no gathered dequantize-GEMM in the reference.
+ *
+ * C_dst is a HOST array of n_dst (1..8) device pointers.  ldc and col0 must be multiples of 8, and from the
+ * token count at which the weights are dequantised once (1024) N must be a multiple of 64.  Everything else as
+ * qgemm_w4a16 (batch 1, scalar zero point, sequential nibbles); the workspace size is qgemm_w4a16_workspace_bytes.
+ * The call returns when the kernels are queued; a destination buffer is complete on its GPU once EVERY rank's
+ * call has finished, which the ranks establish among themselves (a stream-ordered barrier, for example a small
+ * all-reduce).  No kernel waits for another GPU.
+ */
+int qgemm_w4a16_gather(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group,
+                       void* const* C_dst, int n_dst, int64_t ldc, int64_t col0, void* workspace,
+                       int64_t workspace_bytes, int64_t M, int64_t N, int64_t K, int a_dtype, int out_dtype,
+                       uint32_t* status, void* stream);
+
+/*
+ * Mapping a buffer of another process on the same node into this one, for qgemm_w4a16_gather (no counterpart
+ * in the reference, whose SHMEM library owns its symmetric heap).  qgemm_ipc_export fills a
+ * QGEMM_IPC_HANDLE_BYTES-byte handle for the device allocation that holds dev_ptr, and the byte offset of
+ * dev_ptr inside it; the handle and offset travel to the peer by any host channel; there qgemm_ipc_open maps
+ * the allocation and returns its base (add the offset); qgemm_ipc_close unmaps it.  The exporting process
+ * must keep the allocation alive while it is mapped elsewhere.
+ */
+#define QGEMM_IPC_HANDLE_BYTES 64
+int qgemm_ipc_export(const void* dev_ptr, void* handle_out, int64_t* offset_out);
+int qgemm_ipc_open(const void* handle, void** base_out);
+int qgemm_ipc_close(void* base);
+
+/*
  * W4A16 dequantize-GEMM that needs no memory from the caller beyond inputs and output.  (No counterpart
  * in the reference: there the wrapper allocates every workspace with torch before the call.)
  *

@@ -1,0 +1,72 @@
+"""Two-GPU test of the column-sharded W4A16 layer (one process per GPU, NCCL): the peer-store form, in which the
+GEMM kernel's epilogue writes this rank's column block into every rank's output buffer, against the CPU oracle
+and against the collective form.  Skipped on a box with a single GPU.
+
+The ranks are child processes that leave between steps, with no kernel or collective in flight; NVLS is off."""
+import datetime
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                          QGEMM_W4_GEMM_MIN_M="64")  # the dequantise-once path already at 64 tokens (small shapes)
+        import torch.distributed as dist
+        from oracle import qgemm_oracle as oc
+        from tilelang_ascend_b200.dist import ColumnShardedW4A16
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120),
+                                device_id=torch.device("cuda", rank))
+        K, N = 1024, 1024
+        _, P, S = oc.make_w4a16_inputs(1, K, N, "float16", 128, seed=7)  # same seed on every rank
+        peer = ColumnShardedW4A16(P, S, 8, 128, peer_stores=True).to("cuda")
+        coll = ColumnShardedW4A16(P, S, 8, 128, peer_stores=False).to("cuda")
+        ok, msg = True, ""
+        for M, dt in [(1, "float16"), (16, "bfloat16"), (40, "float16"), (70, "bfloat16"), (16, "float16")]:
+            A, _, _ = oc.make_w4a16_inputs(M, K, N, dt, 128, seed=100 + M)
+            ref = oc.dequant_gemm_fp16_ref(A, P, dt, S, 8, 128)
+            for rep in range(3):  # both buffer generations, and a generation's second use
+                out = peer(A.cuda())
+                torch.cuda.synchronize()
+                good = torch.allclose(out.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
+                same = torch.equal(out, coll(A.cuda()))
+                if not (good and same and out.shape == (M, N)):
+                    ok, msg = False, f"M={M} {dt} rep {rep}: close to oracle {good}, equal to collective form {same}"
+            loc = peer.forward(A.cuda(), gather=False)
+            if not torch.equal(loc, out[:, peer.n0:peer.n1]):
+                ok, msg = False, f"M={M}: local block differs from the gathered columns"
+        peer.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, ok, msg))
+    except Exception as exc:  # pragma: no cover
+        import traceback
+        q.put((rank, False, traceback.format_exc()))
+
+
+def test_column_sharded_peer_stores_match_oracle_and_collective():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok, _ in res), res

@@ -48,6 +48,12 @@ SIGNATURES = {
     "qgemm_w4a16_ex": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int, _c.c_int,
                                   _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
                                   _c.c_int64, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
+    "qgemm_w4a16_gather": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_int,
+                                      _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
+                                      _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
+    "qgemm_ipc_export": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p]),
+    "qgemm_ipc_open": (_c.c_int, [_c.c_void_p, _c.c_void_p]),
+    "qgemm_ipc_close": (_c.c_int, [_c.c_void_p]),
     "qgemm_w4a16_noalloc": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p,
                                        _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_void_p,
                                        _c.c_void_p]),

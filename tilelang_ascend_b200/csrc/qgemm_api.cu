@@ -175,7 +175,9 @@ int launch_pdl(void (*kernel)(KArgs...), int grid, int threads, int smem, cudaSt
 template <int BN, bool NK, bool BF>
 int launch_w8(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const qg::W8A8Params& p, int grid,
               cudaStream_t s) {
-  qg::w8a8_gemm_kernel<BN, NK, BF><<<grid, qg::W8_THREADS, qg::W8Cfg<BN>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+  qg::W8Dst dst;
+  for (int d = 0; d < 8; ++d) dst.m[d] = tmC;
+  qg::w8a8_gemm_kernel<BN, NK, BF><<<grid, qg::W8_THREADS, qg::W8Cfg<BN>::SMEM_BYTES, s>>>(tmA, tmB, dst, p);
   CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -363,7 +365,7 @@ static int w4a8_fused(const int8_t* A, const uint8_t* qB, int8_t* workspace, int
 
 extern "C" {
 
-int qgemm_version(void) { return 1004; }  // 1.4: + grouped W8A8, activation quantiser, weight formats, fused W4A8
+int qgemm_version(void) { return 1005; }  // 1.5: + group-sum W4A16 kernel, gathered W4A16 (peer stores), IPC helpers
 
 const char* qgemm_last_error(void) { return g_err; }
 
@@ -450,6 +452,8 @@ static int w8a8_impl(const int8_t* A, const int8_t* B, const float* scale_b, con
 
   qg::W8A8Params p;
   p.tma_store = tma_store ? 1 : 0;
+  p.n_dst = 0;
+  p.col0 = 0;
   p.scale_b = scale_b;
   p.scale_a = scale_a;
   p.C = C;
@@ -566,10 +570,18 @@ int64_t qgemm_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   return qgemm_w4a16_batched_workspace_bytes(1, M, N, K);
 }
 
+// Destinations of the gathered form: `n` row-major [M, ldc] buffers (one per rank, peers' buffers mapped into this
+// process), this rank's columns starting at col0.
+struct GatherDst {
+  void* const* dst;
+  int n;
+  int64_t ldc, col0;
+};
+
 // C[b] = A16[b] (f16 [M, K]) x W16[b]^T (f16 [N, K]), fp32 accumulation, f16 / bf16 out: the tile pipeline of
 // the W8A8 kernel on 2-byte elements (K counted in bytes).
 static int w4_f16_gemm(const void* A16, const void* W16, void* C, int64_t batch, int64_t M, int64_t N, int64_t K,
-                       bool bf, uint32_t* status, cudaStream_t s, int sms) {
+                       bool bf, uint32_t* status, cudaStream_t s, int sms, const GatherDst* gd) {
   const int64_t Kb = K * 2;
   CUtensorMap tmA, tmB, tmC;
   {
@@ -586,14 +598,29 @@ static int w4_f16_gemm(const void* A16, const void* W16, void* C, int64_t batch,
     const uint32_t box[3] = {128, (uint32_t)BN, 1};
     if (encode_map(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, W16, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
   }
-  {
+  qg::W8Dst dst;
+  if (gd == nullptr) {
     const uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
     const uint64_t str[2] = {(uint64_t)N * 2, (uint64_t)M * (uint64_t)N * 2};
     const uint32_t box[3] = {64, 32, 1};
     if (encode_map(&tmC, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, C, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
+    for (int d = 0; d < 8; ++d) dst.m[d] = tmC;
+  } else {
+    // one map per destination over its whole [M, ldc] buffer; a tile lands at column col0 + n.  The 64-column
+    // store boxes must not reach into the next rank's columns, hence N % 64 == 0 (checked by the caller).
+    for (int d = 0; d < 8; ++d) {
+      const uint64_t dims[3] = {(uint64_t)gd->ldc, (uint64_t)M, 1};
+      const uint64_t str[2] = {(uint64_t)gd->ldc * 2, (uint64_t)M * (uint64_t)gd->ldc * 2};
+      const uint32_t box[3] = {64, 32, 1};
+      if (encode_map(&dst.m[d], CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, gd->dst[d < gd->n ? d : 0], dims, str, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+        return -1;
+    }
   }
   qg::W8A8Params p;
   memset(&p, 0, sizeof(p));
+  p.n_dst = gd ? gd->n : 0;
+  p.col0 = gd ? (int)gd->col0 : 0;
   p.C = C;
   p.batch = (int)batch;
   p.M = (int)M;
@@ -612,11 +639,11 @@ static int w4_f16_gemm(const void* A16, const void* W16, void* C, int64_t batch,
   p.split_from = p.num_items = p.num_tiles;
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);
   if (BN == 256) {
-    if (bf) qg::w8a8_gemm_kernel<256, true, true, true><<<grid, qg::W8_THREADS, qg::W8Cfg<256>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
-    else qg::w8a8_gemm_kernel<256, true, false, true><<<grid, qg::W8_THREADS, qg::W8Cfg<256>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+    if (bf) qg::w8a8_gemm_kernel<256, true, true, true><<<grid, qg::W8_THREADS, qg::W8Cfg<256>::SMEM_BYTES, s>>>(tmA, tmB, dst, p);
+    else qg::w8a8_gemm_kernel<256, true, false, true><<<grid, qg::W8_THREADS, qg::W8Cfg<256>::SMEM_BYTES, s>>>(tmA, tmB, dst, p);
   } else {
-    if (bf) qg::w8a8_gemm_kernel<128, true, true, true><<<grid, qg::W8_THREADS, qg::W8Cfg<128>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
-    else qg::w8a8_gemm_kernel<128, true, false, true><<<grid, qg::W8_THREADS, qg::W8Cfg<128>::SMEM_BYTES, s>>>(tmA, tmB, tmC, p);
+    if (bf) qg::w8a8_gemm_kernel<128, true, true, true><<<grid, qg::W8_THREADS, qg::W8Cfg<128>::SMEM_BYTES, s>>>(tmA, tmB, dst, p);
+    else qg::w8a8_gemm_kernel<128, true, false, true><<<grid, qg::W8_THREADS, qg::W8Cfg<128>::SMEM_BYTES, s>>>(tmA, tmB, dst, p);
   }
   CUDA_OK(cudaGetLastError());
   return 0;
@@ -632,7 +659,7 @@ int qgemm_w4a16(const void* A, const uint8_t* B_packed, const void* scales, int 
 static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
                       void* workspace, int64_t workspace_bytes, int64_t batch, int64_t M, int64_t N, int64_t K,
                       int a_dtype, int out_dtype, uint32_t* status, void* stream, const void* zeros, int zero_mode,
-                      int weight_format);
+                      int weight_format, const GatherDst* gd = nullptr);
 
 int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
                         void* workspace, int64_t workspace_bytes, int64_t batch, int64_t M, int64_t N, int64_t K,
@@ -663,11 +690,11 @@ int qgemm_w4a16_ex(const void* A, const uint8_t* B_packed, const void* scales, c
 static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group, void* C,
                       void* workspace, int64_t workspace_bytes, int64_t batch, int64_t M, int64_t N, int64_t K,
                       int a_dtype, int out_dtype, uint32_t* status, void* stream, const void* zeros, int zero_mode,
-                      int weight_format) {
+                      int weight_format, const GatherDst* gd) {
   if (batch <= 0 || batch > 65535) return fail("qgemm_w4a16: batch must be in 1..65535 (got %lld)", (long long)batch);
   if (M <= 0 || N <= 0 || K <= 0) return fail("qgemm_w4a16: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M, (long long)N, (long long)K);
   if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return fail("qgemm_w4a16: dimension too large");
-  if (A == nullptr || B_packed == nullptr || C == nullptr) return fail("qgemm_w4a16: A, B_packed and C must not be null");
+  if (A == nullptr || B_packed == nullptr || (C == nullptr && gd == nullptr)) return fail("qgemm_w4a16: A, B_packed and C must not be null");
   if (a_dtype != QGEMM_DT_F16 && a_dtype != QGEMM_DT_BF16) return fail("qgemm_w4a16: a_dtype must be F16 or BF16 (got %d)", a_dtype);
   if (out_dtype != QGEMM_DT_F16 && out_dtype != QGEMM_DT_BF16) return fail("qgemm_w4a16: out_dtype must be F16 or BF16 (got %d)", out_dtype);
   if (K % 32 != 0) return fail("qgemm_w4a16: K must be a multiple of 32 (got %lld)", (long long)K);
@@ -690,7 +717,8 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
   int sms = 0;
   if (ensure_device(&sms)) return -1;
   const bool use_gs = !dequant_once && w4_gs_shape_ok(M, scales != nullptr, group, K);
-  const int mt = w4_pick_mt(M, use_gs);
+  int mt = w4_pick_mt(M, use_gs);
+  if (gd != nullptr && mt < 16) mt = 16;  // the register-operand decode kernel writes one destination only
 
   CUtensorMap tmW, tmS, tmA;
   memset(&tmS, 0, sizeof(tmS));
@@ -720,6 +748,15 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
 
   qg::W4A16Params p;
   p.C = C;
+  p.n_dst = 0;
+  p.ldc = p.col0 = 0;
+  for (int d = 0; d < 8; ++d) p.c_dst[d] = nullptr;
+  if (gd != nullptr) {
+    p.n_dst = gd->n;
+    p.ldc = (int)gd->ldc;
+    p.col0 = (int)gd->col0;
+    for (int d = 0; d < gd->n; ++d) p.c_dst[d] = gd->dst[d];
+  }
   p.ws_counters = static_cast<uint32_t*>(workspace);
   p.ws_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kW4CounterBytes);
   p.M = (int)M;
@@ -778,13 +815,13 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
                                                              reinterpret_cast<uint4*>(w16), n_chunks, (int)(K / 32),
                                                              (int)N, (int)K, (int)geff, zero);
     CUDA_OK(cudaGetLastError());
-    return w4_f16_gemm(a_prepared, w16, C, batch, M, N, K, bf, status, s, sms);
+    return w4_f16_gemm(a_prepared, w16, C, batch, M, N, K, bf, status, s, sms, gd);
   }
   if (use_gs) {
     if (mt == 16) return launch_w4g<16>(bf, tmW, tmS, tmA, p, (int)grid, s);
     return launch_w4g<32>(bf, tmW, tmS, tmA, p, (int)grid, s);
   }
-  if (w4_use_decode(M) && mt <= 16 && M <= w4_decode_max_m()) {
+  if (gd == nullptr && w4_use_decode(M) && mt <= 16 && M <= w4_decode_max_m()) {
     if (scales == nullptr) return launch_w4d<0>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);
     if (group >= 128) return launch_w4d<4>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);
     if (group == 64) return launch_w4d<2>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);
@@ -796,6 +833,67 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     case 64: return launch_w4<64>(bf, tmW, tmS, tmA, p, (int)grid, s);
     default: return launch_w4<128>(bf, tmW, tmS, tmA, p, (int)grid, s);
   }
+}
+
+int qgemm_w4a16_gather(const void* A, const uint8_t* B_packed, const void* scales, int zero, int64_t group,
+                       void* const* C_dst, int n_dst, int64_t ldc, int64_t col0, void* workspace,
+                       int64_t workspace_bytes, int64_t M, int64_t N, int64_t K, int a_dtype, int out_dtype,
+                       uint32_t* status, void* stream) {
+  if (C_dst == nullptr || n_dst < 1 || n_dst > 8) return fail("qgemm_w4a16_gather: 1 to 8 destinations required (got %d)", n_dst);
+  for (int d = 0; d < n_dst; ++d)
+    if (C_dst[d] == nullptr || !aligned16(C_dst[d])) return fail("qgemm_w4a16_gather: destination %d is null or not 16-byte aligned", d);
+  if (ldc <= 0 || ldc > (1ll << 30) || col0 < 0 || N <= 0 || col0 + N > ldc)
+    return fail("qgemm_w4a16_gather: columns [%lld, %lld) do not fit in rows of %lld", (long long)col0, (long long)(col0 + N), (long long)ldc);
+  if (ldc % 8 != 0 || col0 % 8 != 0) return fail("qgemm_w4a16_gather: ldc and col0 must be multiples of 8 (got %lld, %lld)", (long long)ldc, (long long)col0);
+  if (w4_use_f16_gemm(M, N) && N % 64 != 0)
+    return fail("qgemm_w4a16_gather: from %lld tokens on N must be a multiple of 64 (got %lld)", (long long)w4_gemm_min_m(), (long long)N);
+  GatherDst gd{C_dst, n_dst, ldc, col0};
+  return w4a16_impl(A, B_packed, scales, zero, group, nullptr, workspace, workspace_bytes, 1, M, N, K, a_dtype, out_dtype,
+                    status, stream, nullptr, QGEMM_ZERO_ORIGINAL, QGEMM_W4_SEQUENTIAL, &gd);
+}
+
+// ---- mapping another process's buffer into this one (same node), for the gathered form ----
+static_assert(sizeof(cudaIpcMemHandle_t) == QGEMM_IPC_HANDLE_BYTES, "IPC handle size");
+
+int qgemm_ipc_export(const void* dev_ptr, void* handle_out, int64_t* offset_out) {
+  if (dev_ptr == nullptr || handle_out == nullptr || offset_out == nullptr) return fail("qgemm_ipc_export: null argument");
+  int sms = 0;
+  if (ensure_device(&sms)) return -1;
+  // the handle names the whole allocation the pointer lies in; the pointer's offset inside it travels with it
+  using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn range_fn = nullptr;
+  if (range_fn == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    CUDA_OK(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return fail("cuMemGetAddressRange not available from the driver");
+    range_fn = reinterpret_cast<RangeFn>(fn);
+  }
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  const CUresult r = range_fn(&base, &size, reinterpret_cast<CUdeviceptr>(dev_ptr));
+  if (r != CUDA_SUCCESS) return fail("cuMemGetAddressRange failed with CUresult %d", (int)r);
+  cudaIpcMemHandle_t h;
+  CUDA_OK(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+  memcpy(handle_out, &h, sizeof(h));
+  *offset_out = (int64_t)(reinterpret_cast<CUdeviceptr>(dev_ptr) - base);
+  return 0;
+}
+
+int qgemm_ipc_open(const void* handle, void** base_out) {
+  if (handle == nullptr || base_out == nullptr) return fail("qgemm_ipc_open: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* ptr = nullptr;
+  CUDA_OK(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  *base_out = ptr;
+  return 0;
+}
+
+int qgemm_ipc_close(void* base) {
+  if (base == nullptr) return 0;
+  CUDA_OK(cudaIpcCloseMemHandle(base));
+  return 0;
 }
 
 int qgemm_unpack_int4(const uint8_t* B_packed, int8_t* out, int64_t N, int64_t K, int signed_nibbles,

@@ -45,6 +45,12 @@ struct W4A16Params {
   long long total_items;
   uint32_t* status;
   unsigned long long wait_limit_ns;
+  // Gathered form (column-sharded weights, one process per GPU): when n_dst > 0 the [M, N] result is written
+  // into columns [col0, col0 + N) of n_dst row-major [M, ldc] buffers, one per rank (this rank's own and its
+  // peers', mapped into this process), instead of into C.  Plain stores to peer memory: the transfer of the
+  // output overlaps the rest of the GEMM tile by tile, and no collective has to move it afterwards.
+  void* c_dst[8];
+  int n_dst, ldc, col0;
 };
 
 constexpr int W4_BN = 128;        // weight rows per tile
@@ -91,6 +97,18 @@ __device__ __forceinline__ void w4_tile_coords(const W4A16Params& p, int tile, i
   const int t = tile - b * per_batch;
   n0 = (t / p.m_tiles) * 128;
   m0 = (t % p.m_tiles) * mt;
+}
+
+// One output value C[b][m][n] (or, in the gathered form, column col0 + n of row m of every destination).
+template <bool OUT_BF16>
+__device__ __forceinline__ void w4_store_out(const W4A16Params& p, uint16_t* Cout, int m, int n, float v) {
+  const uint16_t h = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+  if (p.n_dst == 0) {
+    Cout[(size_t)m * p.N + n] = h;
+  } else {
+    const size_t off = (size_t)m * p.ldc + p.col0 + n;
+    for (int d = 0; d < p.n_dst; ++d) reinterpret_cast<uint16_t*>(p.c_dst[d])[off] = h;
+  }
 }
 
 struct W4SegIter {
@@ -280,7 +298,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
     mbar_init(drain, 1);
     *abort_flag = 0;
-    *epi_flag = 0;
+    epi_flag[0] = epi_flag[1] = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmA);
@@ -445,7 +463,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int q = warp & 3;
     const int nl = q * 32 + lane;  // weight row inside the tile == TMEM lane
     pdl_wait();  // the arrival counters are zeroed by the pre-pass kernel in front of this one
-    int it = 0;
+    int it = 0, seg_idx = 0;
     constexpr bool ROUND_ROBIN_E = (WS % Cfg::MMAW) == 0 && (AS % Cfg::MMAW) == 0;  // as in the MMA issuers
     long long first_slab = 0;  // CTA-local index of the segment's first slab: issuer (first_slab + i) % MMAW took slab i
     while (seg.next(tile, ks0, ks1)) {
@@ -489,8 +507,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
                 const int m = m0 + c * CH + j;
                 if (m < p.M) {
                   const float v = __uint_as_float(r[j]);
-                  Cout[(size_t)m * p.N + n] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
-                                                       : __half_as_ushort(__float2half_rn(v));
+                  w4_store_out<OUT_BF16>(p, Cout, m, n, v);
                 }
               }
             }
@@ -504,32 +521,34 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[buf]);
       }
-      if (full_tile) {
-        if (!ok) break;
-        continue;
-      }
-      // Split tile: publish the partial, count arrivals; the last contributor reduces in a fixed order.
+      // Segment end.  The four epilogue warps decide together whether to go on (a warp that left alone would
+      // leave the others waiting at the named barrier for ever): a wait that gave up set the abort flag before its
+      // warp reached the barrier below; one thread reads the flag once and publishes it, with the split-K
+      // verdict, in a control word that alternates between two slots by segment, so that a fast warp's next
+      // write cannot overtake a slow warp's read.
+      const int par = seg_idx & 1;
+      ++seg_idx;
       const long long first_item = (long long)tile * p.KS;
-      const int b_first = w4_owner(T, G, first_item);
-      const int b_last = w4_owner(T, G, first_item + p.KS - 1);
-      __threadfence();
+      int b_first = 0, b_last = 0;
+      if (!full_tile) {
+        b_first = w4_owner(T, G, first_item);
+        b_last = w4_owner(T, G, first_item + p.KS - 1);
+        __threadfence();
+      }
       w4_epi_bar();
       if (warp == 3 && lane == 0) {
-        uint32_t last = 0;
-        if (!*abort_flag) {
+        uint32_t ctrl = *abort_flag ? 1u : 0u;
+        if (!ctrl && !full_tile) {
+          // split tile: count arrivals; the last contributor reduces in a fixed order
           const uint32_t old = atomicAdd(p.ws_counters + b_first, 1u);
-          if (old == (uint32_t)(b_last - b_first)) {
-            last = 1;
-            p.ws_counters[b_first] = 0;  // every contributor has arrived: leave the counter clean
-          }
+          if (old == (uint32_t)(b_last - b_first)) ctrl |= 2u;
         }
-        *epi_flag = last;
+        epi_flag[par] = ctrl;
       }
       w4_epi_bar();
-      const bool is_last = *epi_flag != 0;
-      const bool aborted = *abort_flag != 0;
-      w4_epi_bar();  // epi_flag may be rewritten only after everyone has read it
-      if (aborted) break;
+      const uint32_t ctrl = epi_flag[par];
+      if (ctrl & 1u) break;
+      const bool is_last = (ctrl & 2u) != 0;
       if (is_last) {
         __threadfence();
         if (n < p.N) {
@@ -556,8 +575,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 #pragma unroll
             for (int u = 0; u < RU; ++u) {
               if (mb + u < rows)
-                Cout[(size_t)(m0 + mb + u) * p.N + n] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum[u]))
-                                                                : __half_as_ushort(__float2half_rn(sum[u]));
+                w4_store_out<OUT_BF16>(p, Cout, m0 + mb + u, n, sum[u]);
             }
           }
         }

@@ -473,8 +473,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             for (int j = 0; j < MT; ++j) {
               const int m = m0 + j;
               if (m < p.M)
-                Cout[(size_t)m * p.N + n] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(psum[j]))
-                                                     : __half_as_ushort(__float2half_rn(psum[j]));
+                w4_store_out<OUT_BF16>(p, Cout, m, n, psum[j]);
             }
           }
         } else {
@@ -524,8 +523,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 #pragma unroll
             for (int u = 0; u < 16; ++u) {
               if (mb + u < rows)
-                Cout[(size_t)(m0 + mb + u) * p.N + n] = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sum[u]))
-                                                                 : __half_as_ushort(__float2half_rn(sum[u]));
+                w4_store_out<OUT_BF16>(p, Cout, m0 + mb + u, n, sum[u]);
             }
           }
         }

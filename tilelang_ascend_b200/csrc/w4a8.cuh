@@ -17,7 +17,7 @@ namespace qg {
 struct W4A8Params {
   int* C;                // [M, N] int32
   int* ws_partials;      // scratch: 2 * grid slots of [MT][128] int32
-  uint32_t* ws_counters; // scratch: grid counters, zero on entry, left zero on exit
+  uint32_t* ws_counters; // scratch: grid counters, zeroed by the pre-pass kernel of every call
   const int* row_sums;   // [M] sum_k A[m,k] (signed nibbles only)
   int M, N, K;
   int n_tiles;           // 128-row weight tiles; one token tile (M <= MT)
@@ -126,7 +126,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     }
     mbar_init(drain, 1);
     *abort_flag = 0;
-    *epi_flag = 0;
+    epi_flag[0] = epi_flag[1] = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmA);
@@ -274,7 +274,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     constexpr int CH = Cfg::CH;
     const int q = warp & 3;
     const int nl = q * 32 + lane;  // weight row inside the tile == TMEM lane
-    int it = 0;
+    int it = 0, seg_idx = 0;
     long long first_slab = 0;  // CTA-local index of the segment's first slab: issuer (first_slab + i) % MMAW took slab i
     pdl_wait();  // row sums and zeroed counters come from the pre-pass kernel
     while (seg.next(tile, ks0, ks1)) {
@@ -326,32 +326,32 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[buf]);
       }
-      if (full_tile) {
-        if (!ok) break;
-        continue;
-      }
-      // Split tile: publish the partial, count arrivals; the last contributor adds them up.
+      // Segment end.  The four epilogue warps decide together whether to go on (a warp that left alone would
+      // leave the others waiting at the named barrier for ever): one thread reads the abort flag once and
+      // publishes it, with the split-K verdict, in a control word that alternates between two slots by segment.
+      const int par = seg_idx & 1;
+      ++seg_idx;
       const long long first_item = (long long)tile * p.KS;
-      const int b_first = w4_owner(T, G, first_item);
-      const int b_last = w4_owner(T, G, first_item + p.KS - 1);
-      __threadfence();
+      int b_first = 0, b_last = 0;
+      if (!full_tile) {
+        b_first = w4_owner(T, G, first_item);
+        b_last = w4_owner(T, G, first_item + p.KS - 1);
+        __threadfence();
+      }
       w4_epi_bar();
       if (warp == 3 && lane == 0) {
-        uint32_t last = 0;
-        if (!*abort_flag) {
+        uint32_t ctrl = *abort_flag ? 1u : 0u;
+        if (!ctrl && !full_tile) {
+          // split tile: count arrivals; the last contributor adds the partials up
           const uint32_t old = atomicAdd(p.ws_counters + b_first, 1u);
-          if (old == (uint32_t)(b_last - b_first)) {
-            last = 1;
-            p.ws_counters[b_first] = 0;  // every contributor has arrived: leave the counter clean
-          }
+          if (old == (uint32_t)(b_last - b_first)) ctrl |= 2u;
         }
-        *epi_flag = last;
+        epi_flag[par] = ctrl;
       }
       w4_epi_bar();
-      const bool is_last = *epi_flag != 0;
-      const bool aborted = *abort_flag != 0;
-      w4_epi_bar();  // epi_flag may be rewritten only after everyone has read it
-      if (aborted) break;
+      const uint32_t ctrl = epi_flag[par];
+      if (ctrl & 1u) break;
+      const bool is_last = (ctrl & 2u) != 0;
       if (is_last) {
         __threadfence();
         if (n < p.N) {

@@ -34,6 +34,14 @@ struct W8A8Params {
   // twice as many SMs busy for about half as long.  num_items = num_tiles when nothing is split.
   int split_from, num_items;
   int tma_store;  // C is written with tiled bulk stores from a shared-memory staging tile (needs bn % 64 == 0)
+  // Gathered form: n_dst > 0 destinations (tensor maps in the kernel's W8Dst argument, one [M, ldc] buffer per
+  // rank) receive every tile at column col0 + n instead of the single C.
+  int n_dst, col0;
+};
+
+// Output tensor maps of the gathered form (unused entries are copies of the first).
+struct W8Dst {
+  CUtensorMap m[8];
 };
 
 // One output tile's coordinates: batch index of B / scale_b, batch index of A / C / scale_a, first row, valid rows.
@@ -108,8 +116,9 @@ __device__ __forceinline__ W8Tile w8_tile(const W8A8Params& p, int item) {
 template <int BN, bool B_NK, bool OUT_BF16, bool F16 = false>
 __global__ void __launch_bounds__(W8_THREADS, 1)
 w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, const W8A8Params p) {
+                 const __grid_constant__ W8Dst tmCs, const W8A8Params p) {
   using Cfg = W8Cfg<BN>;
+  const CUtensorMap& tmC = tmCs.m[0];
   constexpr int STAGES = Cfg::STAGES;
 
   extern __shared__ uint8_t smem_raw[];
@@ -364,7 +373,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async_smem();  // this thread's staging writes are visible to the bulk-copy engine
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(&tmC, my_stage, t.n0 + c2 * 32, t.m0 + q * 32, t.bA);
+            if (p.n_dst == 0) {
+              tma_store_3d(&tmC, my_stage, t.n0 + c2 * 32, t.m0 + q * 32, t.bA);
+            } else {
+              for (int d = 0; d < p.n_dst; ++d) tma_store_3d(&tmCs.m[d], my_stage, p.col0 + t.n0 + c2 * 32, t.m0 + q * 32, 0);
+            }
             bulk_commit_group();
           }
         }

@@ -5,13 +5,17 @@
   the full tensor on every rank.
 * W4A16 with a large output dimension: weight columns (rows of ``B_packed[N, K/2]`` and columns of
   ``scales[K/g, N]``) shard across ranks, activations are replicated, and the ``[M, N/g]`` output blocks
-  are reassembled with one all-gather (NCCL over NVLink on GPUs, gloo in the CPU tests).
+  are reassembled on every rank: on the GPUs of one node by the GEMM kernel itself, which stores its block into
+  every rank's output buffer over NVLink (peer stores from the epilogue, no collective on the data), else with
+  one all-gather (NCCL, or gloo in the CPU tests).
 
 * Grouped (ragged) W8A8: whole groups (experts) shard across ranks; each rank holds its experts' weights and
   scales and receives only its groups' rows, so again no collective on the data path.
 
-No kernel reads another GPU's memory: operands are resident on their rank, only outputs move.
-The reference has no counterpart (its only multi-device code is one-sided SHMEM demos).
+No kernel reads another GPU's memory or waits for another GPU: operands are resident on their rank, only
+outputs move, as plain stores.  The reference's multi-device code is its one-sided SHMEM demos
+(examples/shmem/shmem_mm_test_put_nbi.py:69-74: a GEMM followed by a put of its result), which is the
+pattern the peer-store form fuses into the GEMM's epilogue.
 """
 from __future__ import annotations
 
@@ -44,11 +48,22 @@ class ColumnShardedW4A16:
     """W4A16 linear layer whose output features are split over the ranks of a process group.
 
     Holds this rank's rows of ``B_packed`` and columns of ``scales`` (made contiguous once, at load).
-    ``forward(A)`` runs the local GEMM and, unless ``gather=False``, all-gathers the column blocks into the
-    full ``[M, N]`` output on every rank."""
+    ``forward(A)`` runs the local GEMM and, unless ``gather=False``, leaves the full ``[M, N]`` output on every rank.
+
+    Two ways of assembling it:
+
+    * peer stores (CUDA ranks of one node, the default there): every rank owns a full ``[M, N]`` buffer, the
+      buffers are mapped into all processes once per token count, and the GEMM kernel's epilogue writes this
+      rank's column block into every rank's buffer itself.  The output crosses NVLink while the GEMM still runs,
+      nothing is re-arranged afterwards, and the only collective left is a one-element all-reduce that tells a
+      rank when all blocks have landed.  Two buffers alternate, so a rank may still read one result while its
+      peers already write the next.
+    * collective (``peer_stores=False``, CPU / gloo, or when mapping fails): one all-gather of the ``[M, N/g]``
+      blocks and a copy into column order (no copy for a single token, whose blocks are already in order)."""
 
     def __init__(self, B_packed: torch.Tensor, scales: Optional[torch.Tensor], zero: int = 8, group_size: int = 128,
-                 group: Optional[dist.ProcessGroup] = None, gemm: Optional[Callable] = None, multiple: int = 128):
+                 group: Optional[dist.ProcessGroup] = None, gemm: Optional[Callable] = None, multiple: int = 128,
+                 peer_stores="auto"):
         self.pg = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -59,9 +74,15 @@ class ColumnShardedW4A16:
         self.B_local = B_packed[self.n0:self.n1].contiguous()
         self.s_local = None if scales is None else scales[:, self.n0:self.n1].contiguous()
         self.zero, self.group_size = zero, group_size
+        self._custom_gemm = gemm is not None
         if gemm is None:
             from .ops import w4a16_gemm as gemm
         self._gemm = gemm
+        self.peer_stores = peer_stores
+        self._peers = {}    # (M, dtype) -> [generation 0, generation 1], each (own buffer, [address per rank])
+        self._gen = {}
+        self._opened = []   # (base address, device) of every mapping of a peer's allocation
+        self._token = None  # one element, all-reduced as the "all blocks have landed" barrier
 
     def to(self, device):
         self.B_local = self.B_local.to(device)
@@ -69,13 +90,75 @@ class ColumnShardedW4A16:
             self.s_local = self.s_local.to(device)
         return self
 
+    # ---------------------------------------------------------------- peer-store plumbing
+    def _use_peers(self, A) -> bool:
+        if self.peer_stores is False or self._custom_gemm or self.world == 1 or self.world > 8 or not A.is_cuda:
+            return False
+        return (self.n1 - self.n0) % 64 == 0 and self.N % 8 == 0
+
+    def _peer_buffers(self, M, dtype, device):
+        key = (M, dtype)
+        if key not in self._peers:
+            from .ops import ipc_export, ipc_open
+            gens = []
+            for _ in range(2):
+                buf = torch.empty((M, self.N), dtype=dtype, device=device)
+                infos = [None] * self.world
+                dist.all_gather_object(infos, ipc_export(buf), group=self.pg)
+                ptrs = []
+                for r, (handle, off) in enumerate(infos):
+                    if r == self.rank:
+                        ptrs.append(buf.data_ptr())
+                    else:
+                        base = ipc_open(handle, device)
+                        self._opened.append((base, device))
+                        ptrs.append(base + off)
+                gens.append((buf, ptrs))
+            self._peers[key] = gens
+            self._gen[key] = 0
+            if self._token is None:
+                self._token = torch.zeros(1, dtype=torch.float32, device=device)
+            dist.barrier(group=self.pg)  # every rank has mapped every buffer before anyone writes
+        return key
+
+    def close(self):
+        """Unmap the peers' buffers (collective: every rank calls it, none may still be writing)."""
+        if self._opened:
+            from .ops import ipc_close
+            torch.cuda.synchronize()
+            dist.barrier(group=self.pg)
+            for base, device in self._opened:
+                ipc_close(base, device)
+            self._opened = []
+            self._peers = {}
+
+    # ---------------------------------------------------------------- forward
     def forward(self, A: torch.Tensor, gather: bool = True) -> torch.Tensor:
+        if gather and self.world > 1 and self._use_peers(A):
+            try:
+                key = self._peer_buffers(A.shape[0], A.dtype, A.device)
+            except Exception as exc:  # mapping is not possible here (no peer access, another allocator): use the collective
+                if self.peer_stores is True:
+                    raise
+                import warnings
+                warnings.warn(f"peer stores are not available ({exc}); gathering with a collective instead")
+                self.peer_stores = False
+            else:
+                from .ops import w4a16_gemm_gather
+                g = self._gen[key]
+                self._gen[key] = g ^ 1
+                buf, ptrs = self._peers[key][g]
+                w4a16_gemm_gather(A, self.B_local, self.s_local, self.zero, self.group_size, ptrs, self.N, self.n0)
+                dist.all_reduce(self._token, group=self.pg)  # in stream order behind the kernel: all blocks have landed
+                return buf
         C_local = self._gemm(A, self.B_local, self.s_local, self.zero, self.group_size)
         if not gather or self.world == 1:
             return C_local
         M, nl = C_local.shape
         parts = torch.empty((self.world * M, nl), dtype=C_local.dtype, device=C_local.device)
         dist.all_gather_into_tensor(parts, C_local, group=self.pg)  # rank r's block lands in rows [r*M, (r+1)*M)
+        if M == 1:
+            return parts.view(1, self.world * nl)  # one token: the blocks are already in column order
         return parts.view(self.world, M, nl).permute(1, 0, 2).reshape(M, self.world * nl)
 
     __call__ = forward

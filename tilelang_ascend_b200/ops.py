@@ -302,6 +302,75 @@ def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None
     return C
 
 
+def w4a16_gemm_gather(A, B_packed, scales, zeros, group_size, dst_ptrs, ldc, col0, out_dtype=None, stream=None,
+                      status=None):
+    """This rank's ``[M, N]`` block of a column-sharded W4A16 layer, written by the kernel into columns
+    ``[col0, col0 + N)`` of every buffer of ``dst_ptrs``: device addresses of row-major ``[M, ldc]`` buffers, this
+    rank's own and its peers' (mapped with ``ipc_open``).  Returns nothing; the buffers are complete once every
+    rank's call has finished (see ``dist.ColumnShardedW4A16``).  Arguments otherwise as ``w4a16_gemm`` (2-D only)."""
+    import ctypes
+    lib = _lib.load()
+    _require_cuda(A, "A")
+    dev = A.device
+    if A.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError(f"Buffer dtype mismatch for parameter A: expected float16 or bfloat16, got {A.dtype}")
+    out_dtype = A.dtype if out_dtype is None else _dt(out_dtype)
+    if A.dim() != 2 or B_packed.dim() != 2:
+        raise ValueError("A must be [M, K] and B_packed [N, K/2]")
+    M, K = A.shape
+    N = B_packed.shape[0]
+    _check_tensor(A, 0, "A", A.dtype, (M, K), dev)
+    _check_tensor(B_packed, 1, "B_packed", torch.uint8, (N, K // 2), dev)
+    if scales is not None:
+        if group_size in (-1, None):
+            group_size = K
+        _check_tensor(scales, 2, "scales", torch.float16, (K // group_size, N), dev)
+    else:
+        zeros, group_size = 0, K
+    if not 1 <= len(dst_ptrs) <= 8:
+        raise ValueError(f"1 to 8 destination buffers required, got {len(dst_ptrs)}")
+    if M == 0:
+        return
+    sh = _stream_handle(stream, dev)
+    ptr_array = (ctypes.c_void_p * len(dst_ptrs))(*[int(x) for x in dst_ptrs])
+    with torch.cuda.device(dev):
+        ws, need = _w4a16_workspace(lib, 1, M, N, K, dev, sh)
+        rc = lib.qgemm_w4a16_gather(A.data_ptr(), B_packed.data_ptr(), _ptr(scales), int(zeros), int(group_size),
+                                    ctypes.cast(ptr_array, ctypes.c_void_p), len(dst_ptrs), int(ldc), int(col0),
+                                    ws.data_ptr(), need, M, N, K, _ABI_DT[A.dtype], _ABI_DT[out_dtype], _ptr(status), sh)
+    _lib.check(rc, "qgemm_w4a16_gather")
+
+
+def ipc_export(t: torch.Tensor):
+    """(handle bytes, byte offset) under which another process of this node can map the device buffer of ``t``."""
+    import ctypes
+    lib = _lib.load()
+    handle = (ctypes.c_ubyte * 64)()
+    off = ctypes.c_int64(0)
+    with torch.cuda.device(t.device):
+        rc = lib.qgemm_ipc_export(t.data_ptr(), ctypes.cast(handle, ctypes.c_void_p), ctypes.cast(ctypes.byref(off), ctypes.c_void_p))
+    _lib.check(rc, "qgemm_ipc_export")
+    return bytes(handle), int(off.value)
+
+
+def ipc_open(handle: bytes, device) -> int:
+    """Map a buffer exported by ``ipc_export`` in another process; returns the base address of its allocation."""
+    import ctypes
+    lib = _lib.load()
+    buf = (ctypes.c_ubyte * 64).from_buffer_copy(handle)
+    base = ctypes.c_void_p(0)
+    with torch.cuda.device(device):
+        rc = lib.qgemm_ipc_open(ctypes.cast(buf, ctypes.c_void_p), ctypes.cast(ctypes.byref(base), ctypes.c_void_p))
+    _lib.check(rc, "qgemm_ipc_open")
+    return int(base.value)
+
+
+def ipc_close(base: int, device):
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        _lib.check(lib.qgemm_ipc_close(base), "qgemm_ipc_close")
+
+
 @functools.lru_cache(maxsize=None)
 def dequant_gemm_fp16_wrapper(M: int, N: int, K: int, block_M: int, block_N: int, block_K: int,
                               input_dtype: str = "float16", output_dtype: str = "float16"):
