@@ -147,33 +147,42 @@ def max_over_ranks(ms, world):
     return float(t.item())
 
 
-def timed(fn_step, steps, warmup, world):
-    """W untimed steps, then exactly K steps between barrier + synchronize, CUDA events, max over ranks."""
+def timed(fn_step, steps, warmup, world, fn_k_steps=None):
+    """W untimed steps, then exactly K steps between barrier + synchronize, CUDA events, max over ranks.
+    `fn_k_steps`, when given, issues all K steps at once (one CUDA graph holding K steps)."""
     for _ in range(warmup):
         fn_step()
     barrier(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps):
-        fn_step()
+    if fn_k_steps is not None:
+        fn_k_steps()
+    else:
+        for _ in range(steps):
+            fn_step()
     e1.record()
     barrier(world)
     return max_over_ranks(e0.elapsed_time(e1), world)
 
 
-def make_graph_step(launch_all, stream):
-    """Capture one step (all its launches) in a CUDA graph on `stream`; fall back to eager launches."""
+def make_graph_step(launch_all, stream, repeat=1):
+    """Capture `repeat` steps (all their launches) in a CUDA graph on `stream`; fall back to eager launches."""
     try:
         with torch.cuda.stream(stream):
-            launch_all()  # warm: workspaces for this stream exist before capture
+            launch_all()  # warm: the library is loaded and set up before capture
         stream.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=stream):
-            launch_all()
+            for _ in range(repeat):
+                launch_all()
         return (lambda: g.replay()), "cuda_graph"
     except Exception as exc:  # pragma: no cover - depends on driver behaviour
         sys.stderr.write(f"[bench] CUDA graph capture failed ({exc}); timing eager launches\n")
-        return launch_all, "eager"
+
+        def eager():
+            for _ in range(repeat):
+                launch_all()
+        return eager, "eager"
 
 
 # ----------------------------------------------------------------------------------------- our arm
@@ -210,11 +219,12 @@ def run_ours(args):
 
     stream = torch.cuda.Stream()
     step, launch_mode = make_graph_step(launch_batched, stream)
+    k_steps, _ = make_graph_step(launch_batched, stream, repeat=args.steps)  # the timed region: K steps, one graph
     step_single, _ = make_graph_step(launch_all, stream)
     bytes_step = LAYERS * w4a16_bytes(**CFG2)
     with torch.cuda.stream(stream):
         with ClockSampler(local) as clk:
-            ms = timed(step, args.steps, args.warmup, world)
+            ms = timed(step, args.steps, args.warmup, world, fn_k_steps=k_steps)
             # keep the sampler fed with the same work for a little longer: the timed region is short
             t_end = time.time() + 0.25
             while time.time() < t_end:
@@ -260,11 +270,11 @@ def run_ours(args):
             "config": {"workload": "BASELINE configs[1]: W4A16 dequantize_gemm decode M=16 K=4096 N=4096 group=128 zero=8 fp16; "
                                    f"one step = {LAYERS} distinct weight sets ({LAYERS * 8.9:.0f} MB > L2, so no L2 flush needed), "
                                    "issued as ONE batched call w4a16_gemm(A[32,M,K], B_packed[32,N,K/2], scales[32,K/g,N])",
-                       "layers_per_step": LAYERS, "launch": launch_mode,
+                       "layers_per_step": LAYERS, "launch": launch_mode + " (the K timed steps are one graph)",
                        "multi_gpu": "replicas only for this config; sharded configs are under suite"},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                         "kernel": "w4a16_gemm_kernel<16,f16>, batch 32 (time includes its w4a16_prepare_activations pre-pass)",
+                         "kernel": "w4a16_gs_kernel<16,f16>, batch 32 (time includes its w4a16_prepare_activations pre-pass)",
                          "us_per_launch": round(launch_us, 3),
                          "algorithmic_bytes_per_launch": bytes_step, "peak_source": peaks_src + " (copy)"},
             "per_layer_launch": per_layer,
@@ -276,6 +286,26 @@ def run_ours(args):
         if cpu_base is not None:
             line["cpu_baseline"] = cpu_base
         if suite is not None:
+            by_key = {e["key"]: e for e in suite if "key" in e}
+            if "cfg3" in by_key:  # the metric's first half: W8A8 prefill TOPS against the int8 tensor roofline
+                c3 = by_key["cfg3"]
+                line["w8a8_prefill"] = {
+                    "config": "BASELINE configs[2]: W8A8 M=4096 K=4096 N=14336, per-token and per-channel fp32 scales, bf16 out",
+                    "tops": c3["tops"], "us_per_launch": round(c3["ms"] * 1e3, 2),
+                    "kernel": "w8a8_gemm_kernel<256, [K,N] B, bf16> (tcgen05 kind::i8)",
+                    "roofline": {"bound": "tensor", "achieved": c3["tops"], "peak": round(2 * peaks["bf16_tflops"], 1),
+                                 "unit": "TOP/s", "frac": c3["frac_of_2x_measured_bf16"],
+                                 "peak_source": "2 x measured bf16 burst (no measured int8 figure is provided)"},
+                    "int8_yardstick": _int8_yardstick(),
+                    "timing": "median of 5 CUDA-graph replays of 10 launches"}
+            # the sharded configurations in one compact table: [ms] per configuration at this rank count
+            line["sharded"] = {"n_gpus": world,
+                               "cfg4_batch_sharded_ms": by_key["cfg4"]["ms"], "cfg4_tops": by_key["cfg4"]["tops"],
+                               "cfg5_column_sharded_ms": {k[6:]: [by_key[k]["ms_compute"], by_key[k]["ms_gathered"]]
+                                                          for k in by_key if k.startswith("cfg5_m")},
+                               "cfg5_columns": "[compute only, with the output gathered on every rank]",
+                               "cfg5_gather": next(by_key[k]["gather"] for k in by_key if k.startswith("cfg5_m")),
+                               "checked_against_oracle": world > 1}
             line["suite"] = suite
         emit(line)
     if world > 1:
@@ -283,47 +313,114 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def _time_rotating(fn_of_idx, n_sets, iters, world):
-    """Median-free simple timing: `iters` launches cycling over `n_sets` input sets, device time per launch."""
-    for i in range(min(3, iters)):
-        fn_of_idx(i % n_sets)
-    barrier(world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(iters):
-        fn_of_idx(i % n_sets)
-    e1.record()
-    barrier(world)
-    return max_over_ranks(e0.elapsed_time(e1), world) / iters
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _time_rotating(fn_of_idx, n_sets, iters, world, repeats=5):
+    """Device time per launch: `iters` launches that cycle over `n_sets` input sets are captured in one CUDA graph
+    (collectives included) on a side stream, the graph is replayed `repeats` times between barriers, each replay
+    timed with CUDA events, max over ranks; the median of the repeats is returned.  Falls back to eager launches
+    when capture is not possible."""
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(min(3, max(n_sets, 2))):  # warm-up: workspaces, peer buffers, NCCL channels exist before capture
+            fn_of_idx(i % n_sets)
+        stream.synchronize()
+        barrier(world)
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(iters):
+                    fn_of_idx(i % n_sets)
+            run = g.replay
+        except Exception as exc:  # pragma: no cover - depends on driver / NCCL behaviour
+            sys.stderr.write(f"[bench] CUDA graph capture failed ({exc}); timing eager launches\n")
+            torch.cuda.synchronize()
+
+            def run():
+                for i in range(iters):
+                    fn_of_idx(i % n_sets)
+        run()
+        stream.synchronize()
+        samples = []
+        for _ in range(repeats):
+            barrier(world)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            run()
+            e1.record(stream)
+            stream.synchronize()
+            barrier(world)
+            samples.append(max_over_ranks(e0.elapsed_time(e1), world) / iters)
+    return statistics.median(samples)
+
+
+def _int8_yardstick():
+    """cuBLASLt's plain int8 GEMM (torch._int_mm, 8192^3) on this GPU, in the same run: a yardstick beside the
+    2 x measured-bf16 denominator, not a target of its own.  Burst = best of 10, sustained = a loop of about 1 s."""
+    try:
+        n = 8192
+        a = torch.randint(-128, 127, (n, n), dtype=torch.int8, device="cuda")
+        b = torch.randint(-128, 127, (n, n), dtype=torch.int8, device="cuda")
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize()
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        reps = max(10, int(1000.0 / best))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        ops = 2.0 * n ** 3
+        return {"what": "torch._int_mm 8192^3 (cuBLASLt int8), same run", "burst_tops": round(ops / best / 1e9, 1),
+                "sustained_tops": round(ops * reps / e0.elapsed_time(e1) / 1e9, 1)}
+    except Exception as exc:  # pragma: no cover
+        return {"unavailable": repr(exc)[:120]}
+
+
+def _fail(msg):
+    sys.stderr.write("[bench] PARITY FAILURE: " + msg + "\n")
+    raise SystemExit(3)
 
 
 def run_suite(q, world, rank, peaks):
-    """The other BASELINE configurations, sharded where they shard.  Device-resident inputs, CUDA events,
-    max over ranks; inputs either exceed L2 or rotate over enough copies to exceed it."""
-    from oracle import qgemm_oracle as oc  # input generators only
-    from tilelang_ascend_b200.dist import ColumnShardedW4A16, shard_batches
-    int8_peak = 2 * peaks["bf16_tflops"]  # no measured int8 figure: 2x the measured bf16 burst
+    """The other BASELINE configurations, sharded where they shard.  Device-resident inputs, CUDA events, max over
+    ranks, launches replayed from CUDA graphs, median of 5 repeats; inputs either exceed L2 or rotate over enough
+    copies to exceed it.  With more than one rank every sharded configuration is first checked against the CPU
+    oracle on a band of its output (exit code 3 on a mismatch)."""
+    from oracle import qgemm_oracle as oc  # input generators, and the checker of the sharded outputs
+    from tilelang_ascend_b200.dist import ColumnShardedW4A16, shard_batches, shard_range
+    int8_peak = 2 * peaks["bf16_tflops"]  # denominator: 2x the measured bf16 burst; the int8 yardstick is reported beside it
     res = []
 
     if world == 1:
         A, B, sa, sb = [t.cuda() for t in oc.make_config_inputs("cfg1")]
         ms = _time_rotating(lambda i: q.quant_matmul(A, B, sb, scale_a=sa, out_dtype="float16"), 1, 50, world)
         ops = 2 * 256 * 1024 * 1024
-        res.append({"config": "cfg1 W8A8 1x256x1024x1024 fp16 (L2-warm, launch-bound)", "ms": round(ms, 5),
+        res.append({"config": "cfg1 W8A8 1x256x1024x1024 fp16 (L2-warm, latency-bound)", "ms": round(ms, 5),
                     "tops": round(ops / ms / 1e9, 2)})
         del A, B
         A, B, sa, sb = [t.cuda() for t in oc.make_config_inputs("cfg3")]
-        ms = _time_rotating(lambda i: q.quant_matmul(A, B, sb, scale_a=sa, out_dtype="bfloat16"), 1, 20, world)
+        ms = _time_rotating(lambda i: q.quant_matmul(A, B, sb, scale_a=sa, out_dtype="bfloat16"), 1, 10, world)
         ops = 2 * 4096 * 4096 * 14336
         res.append({"config": "cfg3 W8A8 4096x4096x14336 bf16", "ms": round(ms, 5), "tops": round(ops / ms / 1e9, 1),
-                    "frac_of_2x_measured_bf16": round(ops / ms / 1e9 / int8_peak, 4)})
+                    "frac_of_2x_measured_bf16": round(ops / ms / 1e9 / int8_peak, 4), "key": "cfg3"})
         del A, B
 
     if world == 1:
         # the step in front of the W8A8 GEMM: per-token activation quantiser, rows x 8192 bf16 (805 MB moved > L2)
         Mq, Nq = 32768, 8192
         X = torch.randn((Mq, Nq), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda()
-        ms = _time_rotating(lambda i: q.act_quant(X), 1, 10, world)
+        ms = _time_rotating(lambda i: q.act_quant(X), 1, 6, world)
         by = 3 * Mq * Nq + 4 * Mq
         res.append({"config": f"act_quant {Mq}x{Nq} bf16 -> int8 + fp32 row scales", "ms": round(ms, 5),
                     "gbs": round(by / ms / 1e6, 1), "frac_of_measured_hbm": round(by / ms / 1e6 / peaks["hbm_gbs"], 4)})
@@ -333,12 +430,12 @@ def run_suite(q, world, rank, peaks):
         # fused W4A8 at decode size on the config-5 weight shape: signed int4 weights, int8 activations, int32 out
         Kq, Nq, Mq = 8192, 28672, 16
         gen = torch.Generator().manual_seed(6)
-        qBs = [torch.randint(0, 256, (Nq, Kq // 2), dtype=torch.uint8, generator=gen).cuda() for _ in range(2)]
+        qBs = [torch.randint(0, 256, (Nq, Kq // 2), dtype=torch.uint8, generator=gen).cuda() for _ in range(3)]
         A8 = torch.randint(-128, 128, (Mq, Kq), dtype=torch.int8, generator=gen).cuda()
         wsq = torch.empty((Nq, Kq), dtype=torch.int8, device="cuda")
         Cq = torch.empty((Mq, Nq), dtype=torch.int32, device="cuda")
         kq = q.w4a8_gemm_cv(Mq, Nq, Kq)
-        ms = _time_rotating(lambda i: kq(A8, qBs[i % 2], wsq, Cq), 2, 20, world)
+        ms = _time_rotating(lambda i: kq(A8, qBs[i], wsq, Cq), 3, 12, world)
         by = Nq * Kq // 2 + Mq * Kq + 4 * Mq * Nq
         res.append({"config": f"W4A8 fused M={Mq} K={Kq} N={Nq} (signed int4 x int8 -> int32)", "ms": round(ms, 5),
                     "gbs": round(by / ms / 1e6, 1), "frac_of_measured_hbm": round(by / ms / 1e6 / peaks["hbm_gbs"], 4)})
@@ -346,11 +443,18 @@ def run_suite(q, world, rank, peaks):
 
     # config 4: batch sharded, no collective
     A, B, sa, sb = oc.make_config_inputs("cfg4")
-    A, B, sa, sb = [t.cuda() for t in shard_batches([A, B, sa, sb], world, rank)]
-    ms = _time_rotating(lambda i: q.quant_matmul(A, B, sb, scale_a=sa, out_dtype="bfloat16"), 1, 20, world)
+    Ah, Bh, sah, sbh = shard_batches([A, B, sa, sb], world, rank)
+    A, B, sa, sb = [t.cuda() for t in (Ah, Bh, sah, sbh)]
+    if world > 1:  # this rank's first batch entry, a band of rows, bit for bit against the oracle
+        got = q.quant_matmul(A, B, sb, scale_a=sa, out_dtype="bfloat16")[0, 100:164].cpu()
+        want = oc.quant_matmul_ref(Ah[0:1, 100:164], Bh[0:1], sbh[0:1], "bfloat16", scale_a=sah[0:1, 100:164])[0]
+        if not torch.equal(got, want):
+            _fail(f"cfg4 batch shard of rank {rank} differs from the oracle")
+    ms = _time_rotating(lambda i: q.quant_matmul(A, B, sb, scale_a=sa, out_dtype="bfloat16"), 1, 10, world)
     ops = 2 * 16 * 512 * 7168 * 2048
     res.append({"config": f"cfg4 W8A8 16x512x7168x2048 bf16, batch sharded over {world}", "ms": round(ms, 5),
-                "tops": round(ops / ms / 1e9, 1), "frac_of_2x_measured_bf16": round(ops / ms / 1e9 / (world * int8_peak), 4)})
+                "tops": round(ops / ms / 1e9, 1), "frac_of_2x_measured_bf16": round(ops / ms / 1e9 / (world * int8_peak), 4),
+                "key": "cfg4", "checked_against_oracle": world > 1})
     del A, B
 
     if world == 1:
@@ -367,34 +471,60 @@ def run_suite(q, world, rank, peaks):
         sag = (torch.rand(8192, generator=gen) * 0.019 + 0.001).cuda()
         meta = q.build_block_metadata(sizes, 128, "cuda")
         Cg = torch.empty((8192, Ng), dtype=torch.bfloat16, device="cuda")
-        ms = _time_rotating(lambda i: q.grouped_quant_matmul(Ag, Bg, meta, sbg, sag, out_dtype="bfloat16", out=Cg), 1, 20, world)
+        ms = _time_rotating(lambda i: q.grouped_quant_matmul(Ag, Bg, meta, sbg, sag, out_dtype="bfloat16", out=Cg), 1, 10, world)
         ops = 2 * 8192 * Kg * Ng
         res.append({"config": f"grouped W8A8, 16 ragged groups {min(sizes)}..{max(sizes)} rows (8192 total) x 7168 x 2048 bf16",
                     "ms": round(ms, 5), "tops": round(ops / ms / 1e9, 1), "row_blocks": int(meta.shape[0]),
                     "frac_of_2x_measured_bf16": round(ops / ms / 1e9 / int8_peak, 4)})
         del Ag, Bg
 
-    # config 5: weight columns sharded, all-gather of outputs; two weight copies so reads stay L2-cold
+    # config 5: weight columns sharded; the gathered form leaves the whole [M, N] output on every rank.  The weight
+    # copies rotate so that a rank's reads stay L2-cold: enough copies of its shard to exceed 2.5 x L2.
     K, N = 8192, 28672
     _, P, S = oc.make_config_inputs("cfg5", M=1)
-    layers = [ColumnShardedW4A16(P, S, 8, 128).to("cuda"), ColumnShardedW4A16(P.flip(0).contiguous(), S, 8, 128).to("cuda")]
-    del P
+    shard_bytes = (N // world) * K // 2
+    n_sets = max(2, -(-int(2.5 * L2_BYTES) // shard_bytes))
+    layers = [ColumnShardedW4A16(P, S, 8, 128).to("cuda")]
+    for c in range(1, n_sets):  # further copies: the same weights with their rows rolled, one shared set of output buffers
+        layers.append(ColumnShardedW4A16(P.roll(c * 128, 0).contiguous(), S.roll(c * 128, 1).contiguous(), 8, 128,
+                                         share_buffers_with=layers[0]).to("cuda"))
+    n0, n1 = shard_range(N, world, rank, 128)
     for M in (1, 8, 16, 64, 512, 4096):
         g = torch.Generator().manual_seed(M)
-        A = torch.randn((M, K), generator=g).to(torch.bfloat16).cuda()
-        iters = 20 if M <= 512 else 6
-        ms_c = _time_rotating(lambda i: layers[i % 2].forward(A, gather=False), 2, iters, world)
-        ms_g = _time_rotating(lambda i: layers[i % 2].forward(A, gather=True), 2, iters, world) if world > 1 else ms_c
+        Ah = torch.randn((M, K), generator=g).to(torch.bfloat16)
+        A = Ah.cuda()
+        if world > 1:
+            # the gathered output of the first weight copy: a band of this rank's columns and a band of the next
+            # rank's, against the oracle, on a few token rows
+            out = layers[0].forward(A, gather=True)
+            torch.cuda.synchronize()
+            rows = torch.arange(0, M, max(1, M // 8))[:8]
+            nn0 = shard_range(N, world, (rank + 1) % world, 128)[0]
+            cols = torch.cat([torch.arange(n0, n0 + 64), torch.arange(nn0 + 32, nn0 + 96)])
+            want = oc.dequant_gemm_fp16_ref(Ah[rows], P[cols], "bfloat16", S[:, cols].contiguous(), 8, 128)
+            got = out[rows.cuda()][:, cols.cuda()].cpu()
+            if not torch.allclose(got.float(), want.float(), rtol=1e-2, atol=1e-2):
+                _fail(f"cfg5 M={M}: gathered output on rank {rank} differs from the oracle "
+                      f"(max abs diff {(got.float() - want.float()).abs().max().item():.4g})")
+        sets = n_sets if M <= 64 else 2
+        iters = 2 * sets if M <= 512 else 4
+        ms_c = _time_rotating(lambda i: layers[i].forward(A, gather=False), sets, iters, world)
+        ms_g = _time_rotating(lambda i: layers[i].forward(A, gather=True), sets, iters, world) if world > 1 else ms_c
         by = w4a16_bytes(M, K, N, 128)
         fl = 2 * M * K * N
-        entry = {"config": f"cfg5 W4A16 M={M} K=8192 N=28672 bf16, columns sharded over {world}",
-                 "ms_compute": round(ms_c, 5), "ms_with_allgather": round(ms_g, 5),
-                 "gbs": round(by / ms_c / 1e6, 1), "tflops": round(fl / ms_c / 1e9, 1)}
+        entry = {"config": f"cfg5 W4A16 M={M} K=8192 N=28672 bf16, columns sharded over {world}", "key": f"cfg5_m{M}",
+                 "ms_compute": round(ms_c, 5), "ms_gathered": round(ms_g, 5),
+                 "gather": "none (one rank)" if world == 1 else ("peer stores from the GEMM epilogue" if layers[0].peer_stores is not False else "NCCL all-gather + copy"),
+                 "gbs": round(by / ms_c / 1e6, 1), "tflops": round(fl / ms_c / 1e9, 1), "weight_copies_rotated": sets,
+                 "checked_against_oracle": world > 1}
         if M <= 64:
             entry["frac_of_measured_hbm"] = round(by / ms_c / 1e6 / (world * peaks["hbm_gbs"]), 4)
         else:
             entry["frac_of_measured_bf16"] = round(fl / ms_c / 1e9 / (world * peaks["bf16_tflops"]), 4)
         res.append(entry)
+        del A
+    if world > 1:
+        layers[0].close()
     return res
 
 

@@ -62,6 +62,12 @@ int set_smem_w8() {
   if (set_smem(qg::w8a8_gemm_kernel<BN, true, true>, C::SMEM_BYTES)) return -1;
   if (set_smem(qg::w8a8_gemm_kernel<BN, true, false, true>, C::SMEM_BYTES)) return -1;
   if (set_smem(qg::w8a8_gemm_kernel<BN, true, true, true>, C::SMEM_BYTES)) return -1;
+  if (BN == 256) {  // the two-CTA K split
+    if (set_smem(qg::w8a8_gemm_kernel<256, false, false, false, true>, C::SMEM_BYTES)) return -1;
+    if (set_smem(qg::w8a8_gemm_kernel<256, false, true, false, true>, C::SMEM_BYTES)) return -1;
+    if (set_smem(qg::w8a8_gemm_kernel<256, true, false, false, true>, C::SMEM_BYTES)) return -1;
+    if (set_smem(qg::w8a8_gemm_kernel<256, true, true, false, true>, C::SMEM_BYTES)) return -1;
+  }
   return 0;
 }
 template <int FLUSH>
@@ -70,13 +76,6 @@ int set_smem_w4d() {
   if (set_smem(qg::w4a16_decode_kernel<FLUSH, 1, true>, qg::W4DCfg<1>::SMEM_BYTES)) return -1;
   if (set_smem(qg::w4a16_decode_kernel<FLUSH, 2, false>, qg::W4DCfg<2>::SMEM_BYTES)) return -1;
   if (set_smem(qg::w4a16_decode_kernel<FLUSH, 2, true>, qg::W4DCfg<2>::SMEM_BYTES)) return -1;
-  return 0;
-}
-int set_smem_w8_pair() {
-  if (set_smem(qg::w8a8_gemm_pair_kernel<false, false>, qg::W8P_SMEM_BYTES)) return -1;
-  if (set_smem(qg::w8a8_gemm_pair_kernel<false, true>, qg::W8P_SMEM_BYTES)) return -1;
-  if (set_smem(qg::w8a8_gemm_pair_kernel<true, false>, qg::W8P_SMEM_BYTES)) return -1;
-  if (set_smem(qg::w8a8_gemm_pair_kernel<true, true>, qg::W8P_SMEM_BYTES)) return -1;
   return 0;
 }
 template <int MT>
@@ -120,7 +119,7 @@ int ensure_device(int* sm_count) {
       if (qres != cudaDriverEntryPointSuccess || fn == nullptr) return fail("cuTensorMapEncodeTiled not available from the driver");
       g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
-    if (set_smem_w8<128>() || set_smem_w8<256>() || set_smem_w8_pair()) return -1;
+    if (set_smem_w8<128>() || set_smem_w8<256>()) return -1;
     if (set_smem_w4<16>() || set_smem_w4<32>() || set_smem_w4<64>() || set_smem_w4<128>()) return -1;
     if (set_smem_w4g<16>() || set_smem_w4g<32>()) return -1;
     if (set_smem_w4i8<16>() || set_smem_w4i8<32>() || set_smem_w4i8<64>() || set_smem_w4i8<128>()) return -1;
@@ -182,10 +181,25 @@ int launch_w8(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap&
   return 0;
 }
 
+// The K split: clusters of two CTAs, one 128 x 256 tile per cluster.
 template <bool NK, bool BF>
-int launch_w8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const qg::W8A8Params& p, int grid, cudaStream_t s) {
-  qg::w8a8_gemm_pair_kernel<NK, BF><<<grid, qg::W8_THREADS, qg::W8P_SMEM_BYTES, s>>>(tmA, tmB, p);
-  CUDA_OK(cudaGetLastError());
+int launch_w8_splitk(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const qg::W8A8Params& p,
+                     int tiles, cudaStream_t s) {
+  qg::W8Dst dst;
+  for (int d = 0; d < 8; ++d) dst.m[d] = tmC;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * tiles));
+  cfg.blockDim = dim3((unsigned)qg::W8_THREADS);
+  cfg.dynamicSmemBytes = (size_t)qg::W8Cfg<256>::SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUDA_OK(cudaLaunchKernelEx(&cfg, qg::w8a8_gemm_kernel<256, NK, BF, false, true>, tmA, tmB, dst, p));
   return 0;
 }
 
@@ -419,15 +433,15 @@ static int w8a8_impl(const int8_t* A, const int8_t* B, const float* scale_b, con
   }
   const int64_t m_tiles = meta ? num_blocks : (M + 127) / 128;
   const int64_t tiles256 = batchA * m_tiles * ((N + 255) / 256);
-  const int BN = (N > 128 && tiles256 >= sms) ? 256 : 128;
+  // Fewer 256-wide tiles than half the SMs: split K over pairs of CTAs (one tile per pair, twice as many SMs at
+  // work on full-width tiles) instead of falling back to 128-wide tiles.  QGEMM_W8_SPLITK=0 disables it.
+  static const int splitk_on = getenv("QGEMM_W8_SPLITK") ? atoi(getenv("QGEMM_W8_SPLITK")) : 1;
+  const bool use_splitk = splitk_on && meta == nullptr && N > 128 && 2 * tiles256 <= sms && (K + 127) / 128 >= 4;
+  const int BN = (N > 128 && (tiles256 >= sms || use_splitk)) ? 256 : 128;
   // Width actually computed per tile (a multiple of 32, at most BN).  Narrower tiles that fill the last
   // round of the persistent grid better were measured slower on B200 (224 instead of 256 columns on the
   // 4096 x 4096 x 14336 shape: 235 us against 231 us), so the full width is used.
   const int bn_eff = BN;
-  // Pairs of CTAs on 256 x 256 tiles when there is at least one tile per pair and M fills both halves.
-  const int64_t pair_tiles = batch * ((M + 255) / 256) * ((N + 255) / 256);
-  static const int pair_mode = getenv("QGEMM_W8_PAIR") ? atoi(getenv("QGEMM_W8_PAIR")) : 0;
-  const bool use_pair = meta == nullptr && pair_mode != 0 && M >= 256 && N >= 256 && pair_tiles >= sms / 2;
   if (b_layout == QGEMM_B_KN) {
     const uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)batch};
     const uint64_t str[2] = {(uint64_t)N, (uint64_t)K * (uint64_t)N};
@@ -436,7 +450,7 @@ static int w8a8_impl(const int8_t* A, const int8_t* B, const float* scale_b, con
   } else {
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)batch};
     const uint64_t str[2] = {(uint64_t)K, (uint64_t)N * (uint64_t)K};
-    const uint32_t box[3] = {128, (uint32_t)(use_pair ? 128 : BN), 1};
+    const uint32_t box[3] = {128, (uint32_t)BN, 1};
     if (encode_map(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -1;
   }
 
@@ -490,15 +504,9 @@ static int w8a8_impl(const int8_t* A, const int8_t* B, const float* scale_b, con
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool nk = b_layout == QGEMM_B_NK;
   const bool bf = out_dtype == QGEMM_DT_BF16;
-  if (use_pair) {
-    p.m_tiles = (int)((M + 255) / 256);
-    p.n_tiles = (int)((N + 255) / 256);
-    p.bn = 256;
-    p.num_tiles = (int)pair_tiles;
-    const int64_t pairs = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
-    const int pgrid = (int)(2 * pairs);
-    if (nk) return bf ? launch_w8_pair<true, true>(tmA, tmB, p, pgrid, s) : launch_w8_pair<true, false>(tmA, tmB, p, pgrid, s);
-    return bf ? launch_w8_pair<false, true>(tmA, tmB, p, pgrid, s) : launch_w8_pair<false, false>(tmA, tmB, p, pgrid, s);
+  if (use_splitk) {
+    if (nk) return bf ? launch_w8_splitk<true, true>(tmA, tmB, tmC, p, (int)num_tiles, s) : launch_w8_splitk<true, false>(tmA, tmB, tmC, p, (int)num_tiles, s);
+    return bf ? launch_w8_splitk<false, true>(tmA, tmB, tmC, p, (int)num_tiles, s) : launch_w8_splitk<false, false>(tmA, tmB, tmC, p, (int)num_tiles, s);
   }
   if (BN == 256) {
     if (nk) return bf ? launch_w8<256, true, true>(tmA, tmB, tmC, p, grid, s) : launch_w8<256, true, false>(tmA, tmB, tmC, p, grid, s);

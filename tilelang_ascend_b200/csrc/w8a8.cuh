@@ -113,11 +113,20 @@ __device__ __forceinline__ W8Tile w8_tile(const W8A8Params& p, int item) {
 // F16 = true runs the same pipeline on f16 operands (kind::f16, fp32 accumulators, no scales): one MMA K step
 // is 32 bytes for both element types, so with K counted in bytes (p.K, p.k_blocks) nothing else changes.  It
 // serves the large-token W4A16 path, whose weights are dequantised to f16 once and then multiplied here.
-template <int BN, bool B_NK, bool OUT_BF16, bool F16 = false>
+//
+// SPLITK = true is the form for grids that would leave more than half of the SMs idle (fewer 128 x 256 tiles than
+// half the SM count): the kernel is launched in clusters of two CTAs, one tile per cluster; each CTA accumulates
+// one half of the K range in its own tensor memory, CTA 1 then writes its int32 accumulators into CTA 0's shared
+// memory (the pipeline stages, idle by then) through distributed shared memory, and CTA 0 adds them in its
+// epilogue - an exact integer sum, so the result is bit-identical to the unsplit kernel's.  The counterpart in the
+// reference is the K split of examples/gemm_splitk/example_tilelang_gemm_splitk.py:15-48, whose partial tiles meet
+// in global memory through atomic adds (src/tl_templates/ascend/common.h:249-259).
+template <int BN, bool B_NK, bool OUT_BF16, bool F16 = false, bool SPLITK = false>
 __global__ void __launch_bounds__(W8_THREADS, 1)
 w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ W8Dst tmCs, const W8A8Params p) {
   using Cfg = W8Cfg<BN>;
+  static_assert(!(SPLITK && F16), "the split form adds int32 partial sums");
   const CUtensorMap& tmC = tmCs.m[0];
   constexpr int STAGES = Cfg::STAGES;
 
@@ -130,17 +139,27 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tfull = bars + 2 * STAGES;
   uint64_t* tempty = tfull + 2;
   uint64_t* drain = tempty + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
+  uint64_t* stages_free = drain + 1;    // split form, in CTA 1: CTA 0's MMAs have finished reading its stages
+  uint64_t* partial_full = drain + 2;   // split form, in CTA 0: CTA 1's accumulators have arrived
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 3);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // split form: CTA `crank` of the pair takes the k blocks [kb_begin, kb_end) of tile (block index / 2)
+  const int crank = SPLITK ? (int)cluster_ctarank() : 0;
+  const int tile_first = SPLITK ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tile_stride = SPLITK ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int kb_begin = SPLITK ? (crank ? p.k_blocks / 2 : 0) : 0;
+  const int kb_end = SPLITK ? (crank ? p.k_blocks : p.k_blocks / 2) : p.k_blocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
+    mbar_init(stages_free, 4);
+    mbar_init(partial_full, 4);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
       mbar_init(&tempty[i], 4);
@@ -159,6 +178,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  if constexpr (SPLITK) cluster_sync_all();  // both CTAs' barriers exist before either signals the other's
   const uint32_t tmem_base = *tmem_slot;
   const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns};
 
@@ -168,12 +188,12 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0, issued_mask = 0, parity_mask = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_items; tile += gridDim.x) {
+      for (int tile = tile_first; ok && tile < p.num_items; tile += tile_stride) {
         const W8Tile t = w8_tile(p, tile);
         const int m0 = t.m0, n0 = t.n0;
         const int b_boxes = B_NK ? 1 : (t.bn + 127) / 128;  // 128-column boxes of B actually needed
         const uint32_t tx = Cfg::A_BYTES + (B_NK ? (uint32_t)Cfg::B_BYTES : (uint32_t)(b_boxes * W8_BK * 128));
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
           uint8_t* sA = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sB = sA + Cfg::A_BYTES;
@@ -212,7 +232,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_items; tile += gridDim.x, ++it) {
+      for (int tile = tile_first; ok && tile < p.num_items; tile += tile_stride, ++it) {
         const uint32_t bn = (uint32_t)((tile < p.split_from) ? p.bn : (p.bn >> 1));
         const uint32_t idesc = F16 ? make_idesc(ACC_F32, FMT_F16, FMT_F16, 0, B_NK ? 0 : 1, W8_BM, bn)
                                    : make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, B_NK ? 0 : 1, W8_BM, bn);
@@ -221,7 +241,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!mbar_wait(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&full[stage], phase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sA = smem_u32(smem + stage * Cfg::STAGE_BYTES);
@@ -237,8 +257,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               // [K rows][128 B of N]: 32 K rows per MMA = 4096 B; the next 128 columns are one box (16 KB) further.
               bdesc = make_desc_mnmajor(sB + k * (W8_UMMA_K * 128), W8_BK * 128);
             }
-            if constexpr (F16) umma_f16_ss(d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-            else umma_i8_ss(d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (F16) umma_f16_ss(d, adesc, bdesc, idesc, ((kb - kb_begin) | k) != 0 ? 1u : 0u);
+            else umma_i8_ss(d, adesc, bdesc, idesc, ((kb - kb_begin) | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -262,7 +282,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     float* sb_s = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + Cfg::BAR_BYTES) + q * BN;
     uint8_t* my_stage = out_stage + q * 4096;  // [32 rows][128 B], 16-byte piece j of row r at (j ^ (r & 7))
     int it = 0;
-    for (int tile = blockIdx.x; tile < p.num_items; tile += gridDim.x, ++it) {
+    // split form: the other CTA's accumulators travel through CTA 0's pipeline stages, one 16-byte piece per
+    // (row, four columns): piece (col / 4, row) at ((col / 4) * 128 + row) * 16, so that a warp's 32 rows are
+    // 512 contiguous bytes for the sender's stores and the receiver's loads alike
+    const uint32_t part_row = smem_u32(smem) + (uint32_t)(q * 32 + lane) * 16u;
+    for (int tile = tile_first; tile < p.num_items; tile += tile_stride, ++it) {
       const W8Tile t = w8_tile(p, tile);
       const int buf = it & 1;
       const uint32_t tphase = (it >> 1) & 1;
@@ -281,6 +305,48 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE)) break;
       tc_fence_after_sync();
+      if constexpr (SPLITK) {
+        const uint32_t taddr_s = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+        if (crank == 0) {
+          // this CTA's MMAs are done: its stages may be overwritten; then wait for the other half's sums
+          if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(stages_free), 1));
+          bool got = true;
+          if (lane == 0) {
+            const uint64_t t0 = global_timer_ns();
+            while (!mbar_try_wait_cluster(partial_full, 0)) {
+              if (*abort_flag || global_timer_ns() - t0 > p.wait_limit_ns) {
+                *abort_flag = 1u;
+                if (p.status) atomicMax(p.status, (uint32_t)ST_TIMEOUT_EPILOGUE);
+                got = false;
+                break;
+              }
+            }
+          }
+          got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+          if (!got) break;
+          fence_acq_rel_cluster();
+        } else {
+          // wait until CTA 0 has finished with its stages, then send this CTA's accumulators and leave
+          if (!mbar_wait_warp(stages_free, 0, ctl, ST_TIMEOUT_EPILOGUE)) break;
+          const uint32_t dst_row = mapa_u32(part_row, 0);
+#pragma unroll 1
+          for (int c = 0; c < (t.bn >> 5); ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr_s + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              st_cluster_v4(dst_row + (uint32_t)((c * 8 + j) * 128 * 16), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          }
+          fence_acq_rel_cluster();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(partial_full), 0));
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[buf]);
+          continue;
+        }
+      }
       const size_t row_off = ((size_t)t.bA * p.M + (row_ok ? m : 0)) * (size_t)p.N;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
       const int chunks = t.bn >> 5;
@@ -301,6 +367,19 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (c >= chunks) break;
           tmem_ld_wait();                                                     // chunk c is in r[h]
           if (c + 1 < chunks) tmem_ld_32x32b_x32(taddr + (c + 1) * 32, r[h ^ 1]);  // chunk c + 1 in flight
+          if constexpr (SPLITK) {  // add the other CTA's half of the K range (exact: int32)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              uint4 pv;
+              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(pv.x), "=r"(pv.y), "=r"(pv.z), "=r"(pv.w)
+                           : "r"(part_row + (uint32_t)((c * 8 + j) * 128 * 16)));
+              r[h][4 * j] += pv.x;
+              r[h][4 * j + 1] += pv.y;
+              r[h][4 * j + 2] += pv.z;
+              r[h][4 * j + 3] += pv.w;
+            }
+          }
           const int n = t.n0 + c * 32;
           if (row_ok && n < p.N && p.acc_out != nullptr) {
             int4* dst = reinterpret_cast<int4*>(p.acc_out + row_off + n);
@@ -392,237 +471,10 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (SPLITK) cluster_sync_all();  // neither CTA of the pair leaves while the other may still reach into it
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
-  }
-}
-
-// ---------------------------------------------------------------------------------------------------
-// Two-CTA form: a pair of CTAs (a cluster of 2 on neighbouring SMs) computes one 256 x 256 tile with
-// tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and one half (128 columns) of B, so the
-// bytes pulled from L2 per MMA cycle drop by a third compared with the one-CTA 128 x 256 tile, which is what
-// limits that kernel.  Each load goes into the loading CTA's own shared memory; only the completion count
-// lives in the leader's barrier.  The leader CTA (rank 0) issues the MMAs; stage-free and accumulator-ready
-// signals are committed to the barrier of each CTA separately.
-// ---------------------------------------------------------------------------------------------------
-constexpr int W8P_BN = 256;
-constexpr int W8P_STAGES = 6;
-constexpr int W8P_A_BYTES = W8_BM * W8_BK;        // 16 KB: this CTA's 128 rows
-constexpr int W8P_B_BYTES = 128 * W8_BK;          // 16 KB: this CTA's 128 columns of B
-constexpr int W8P_STAGE_BYTES = W8P_A_BYTES + W8P_B_BYTES;
-constexpr int W8P_SMEM_BYTES = W8P_STAGES * W8P_STAGE_BYTES + 256 + 1024;
-constexpr int W8P_GROUP_M = 4;
-
-__device__ __forceinline__ void w8p_decode_tile(const W8A8Params& p, int m2_tiles, int tile, int& b, int& m_blk, int& n_blk) {
-  const int per_batch = m2_tiles * p.n_tiles;
-  b = tile / per_batch;
-  const int r = tile - b * per_batch;
-  const int band = W8P_GROUP_M * p.n_tiles;
-  const int g = r / band;
-  const int first_m = g * W8P_GROUP_M;
-  const int gsz = min(m2_tiles - first_m, W8P_GROUP_M);
-  const int in_band = r - g * band;
-  m_blk = first_m + in_band % gsz;
-  n_blk = in_band / gsz;
-}
-
-// p.m_tiles counts 256-row tiles here; p.num_tiles = batch * m_tiles * n_tiles (n_tiles of 256 columns).
-template <bool B_NK, bool OUT_BF16>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W8_THREADS, 1)
-w8a8_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const W8A8Params p) {
-  constexpr int STAGES = W8P_STAGES;
-  constexpr int BN = W8P_BN;
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * W8P_STAGE_BYTES);
-  uint64_t* full = bars;                 // used in the leader CTA only
-  uint64_t* empty = bars + STAGES;       // one set per CTA
-  uint64_t* tfull = bars + 2 * STAGES;   // one set per CTA
-  uint64_t* tempty = tfull + 2;          // used in the leader CTA only (8 arrivals: 4 epilogue warps x 2 CTAs)
-  uint64_t* drain = tempty + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
-  volatile uint32_t* abort_flag = tmem_slot + 1;
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
-  const bool leader = rank == 0;
-  const int pair = blockIdx.x >> 1;
-  const int n_pairs = gridDim.x >> 1;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 8);
-    }
-    mbar_init(drain, 1);
-    *abort_flag = 0;
-    fence_barrier_init();
-    tma_prefetch_desc(&tmA);
-    tma_prefetch_desc(&tmB);
-  }
-  if (warp == 1) {
-    tmem_alloc_pair(tmem_slot, 512);
-    tmem_relinquish_pair();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  cluster_sync_all();  // the peer's barriers exist before anything is signalled across the pair
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-  const WaitCtl ctl{abort_flag, p.status, p.wait_limit_ns, 0};
-
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer (both CTAs)
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = pair; ok && tile < p.num_tiles; tile += n_pairs) {
-        int b, m_blk, n_blk;
-        w8p_decode_tile(p, p.m_tiles, tile, b, m_blk, n_blk);
-        const int m0 = m_blk * 256 + (int)rank * 128;
-        const int nh = n_blk * BN + (int)rank * 128;  // this CTA's half of the tile's columns
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
-          uint8_t* sA = smem + stage * W8P_STAGE_BYTES;
-          uint8_t* sB = sA + W8P_A_BYTES;
-          const uint32_t full_leader = mapa_u32(smem_u32(&full[stage]), 0);
-          if (leader) mbar_arrive_expect_tx(&full[stage], 2 * W8P_STAGE_BYTES);
-          tma_load_3d_pair(sA, &tmA, full_leader, kb * W8_BK, m0, b);
-          if constexpr (B_NK) tma_load_3d_pair(sB, &tmB, full_leader, kb * W8_BK, nh, b);
-          else tma_load_3d_pair(sB, &tmB, full_leader, nh, kb * W8_BK, b);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-        }
-      }
-      if (!ok) {
-        // Gave up: the completion counts of this CTA's copies live in the leader, so simply leave the
-        // copies already issued a bounded time to land before the CTA may exit.
-        const uint64_t t0 = global_timer_ns();
-        while (global_timer_ns() - t0 < 100000ull) {}
-      }
-    }
-  } else if (warp == 1) {
-    // -------------------------------------------------------------- MMA issuer (leader CTA only)
-    if (leader && lane == 0) {
-      constexpr uint32_t idesc = make_idesc(ACC_S32, FMT_S8, FMT_S8, 0, B_NK ? 0 : 1, 256, BN);
-      int stage = 0;
-      uint32_t phase = 0;
-      int it = 0;
-      bool ok = true;
-      for (int tile = pair; ok && tile < p.num_tiles; tile += n_pairs, ++it) {
-        const int buf = it & 1;
-        const uint32_t tphase = (it >> 1) & 1;
-        if (!mbar_wait(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t d = tmem_base + buf * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(&full[stage], phase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t sA = smem_u32(smem + stage * W8P_STAGE_BYTES);
-          const uint32_t sB = sA + W8P_A_BYTES;
-          const uint64_t a0 = make_desc_kmajor(sA);
-#pragma unroll
-          for (int k = 0; k < W8_BK / W8_UMMA_K; ++k) {
-            const uint64_t adesc = a0 + (uint64_t)((k * W8_UMMA_K) >> 4);
-            uint64_t bdesc;
-            if constexpr (B_NK) bdesc = make_desc_kmajor(sB) + (uint64_t)((k * W8_UMMA_K) >> 4);
-            else bdesc = make_desc_mnmajor(sB + k * (W8_UMMA_K * 128), W8_BK * 128);
-            umma_i8_ss_pair(d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
-          const uint32_t e_local = smem_u32(&empty[stage]);
-          umma_commit_pair(e_local);
-          umma_commit_pair(mapa_u32(e_local, 1));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-        }
-        if (ok) {
-          const uint32_t t_local = smem_u32(&tfull[buf]);
-          umma_commit_pair(t_local);
-          umma_commit_pair(mapa_u32(t_local, 1));
-        }
-      }
-      if (!ok) {
-        umma_commit_pair(smem_u32(drain));
-        const uint64_t t0 = global_timer_ns();
-        while (!mbar_try_wait(drain, 0)) {
-          if (global_timer_ns() - t0 > p.wait_limit_ns) break;
-        }
-      }
-    }
-  } else {
-    // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
-    const int q = warp & 3;
-    int it = 0;
-    for (int tile = pair; tile < p.num_tiles; tile += n_pairs, ++it) {
-      int b, m_blk, n_blk;
-      w8p_decode_tile(p, p.m_tiles, tile, b, m_blk, n_blk);
-      const int buf = it & 1;
-      const uint32_t tphase = (it >> 1) & 1;
-      if (!mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE)) break;
-      tc_fence_after_sync();
-      const int m = m_blk * 256 + (int)rank * 128 + q * 32 + lane;
-      const bool row_ok = m < p.M;
-      float sa = 1.0f;
-      if (p.sa_mode != 0 && row_ok) sa = __ldg(p.scale_a + (p.sa_mode == 2 ? (size_t)b * p.M : 0) + m);
-      const float* sbp = p.scale_b + (p.sb_mode == 2 ? (size_t)b * p.N : 0);
-      const size_t row_off = ((size_t)b * p.M + (row_ok ? m : 0)) * (size_t)p.N;
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int n = n_blk * BN + c * 32;
-        if (row_ok && n < p.N) {
-          if (p.acc_out != nullptr) {
-            int4* dst = reinterpret_cast<int4*>(p.acc_out + row_off + n);
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (n + 4 * j < p.N) dst[j] = make_int4((int)r[4 * j], (int)r[4 * j + 1], (int)r[4 * j + 2], (int)r[4 * j + 3]);
-          }
-          uint16_t* cbase = reinterpret_cast<uint16_t*>(p.C) + row_off + n;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (p.C != nullptr && n + 8 * j < p.N) {
-              uint32_t o[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int col = 8 * j + 2 * e;
-                float s0, s1;
-                if (p.sb_mode == 0) { s0 = s1 = __ldg(sbp); }
-                else { s0 = __ldg(sbp + n + col); s1 = __ldg(sbp + n + col + 1); }
-                float f0 = __int2float_rn((int)r[col]);
-                float f1 = __int2float_rn((int)r[col + 1]);
-                if (p.sa_mode != 0) { f0 = __fmul_rn(f0, sa); f1 = __fmul_rn(f1, sa); }
-                f0 = __fmul_rn(f0, s0);
-                f1 = __fmul_rn(f1, s1);
-                o[e] = pack_out2<OUT_BF16>(f0, f1);
-              }
-              *reinterpret_cast<uint4*>(cbase + 8 * j) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[buf]), 0));
-    }
-  }
-
-  // ------------------------------------------------------------------ teardown
-  tc_fence_before_sync();
-  __syncthreads();
-  cluster_sync_all();  // nothing may still be signalling into a CTA that has left
-  if (warp == 1) {
-    tc_fence_after_sync();
-    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 

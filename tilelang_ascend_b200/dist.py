@@ -63,7 +63,7 @@ class ColumnShardedW4A16:
 
     def __init__(self, B_packed: torch.Tensor, scales: Optional[torch.Tensor], zero: int = 8, group_size: int = 128,
                  group: Optional[dist.ProcessGroup] = None, gemm: Optional[Callable] = None, multiple: int = 128,
-                 peer_stores="auto"):
+                 peer_stores="auto", share_buffers_with: Optional["ColumnShardedW4A16"] = None):
         self.pg = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -83,6 +83,11 @@ class ColumnShardedW4A16:
         self._gen = {}
         self._opened = []   # (base address, device) of every mapping of a peer's allocation
         self._token = None  # one element, all-reduced as the "all blocks have landed" barrier
+        self._owner = self  # the layer whose output buffers this one writes (several layers of one shape, say the
+        if share_buffers_with is not None:  # same projection of different blocks, can share them)
+            if share_buffers_with.N != self.N or share_buffers_with.world != self.world:
+                raise ValueError("layers that share output buffers must have the same N and process group")
+            self._owner = share_buffers_with._owner
 
     def to(self, device):
         self.B_local = self.B_local.to(device)
@@ -97,6 +102,8 @@ class ColumnShardedW4A16:
         return (self.n1 - self.n0) % 64 == 0 and self.N % 8 == 0
 
     def _peer_buffers(self, M, dtype, device):
+        if self._owner is not self:
+            return self._owner._peer_buffers(M, dtype, device)
         key = (M, dtype)
         if key not in self._peers:
             from .ops import ipc_export, ipc_open
@@ -145,11 +152,12 @@ class ColumnShardedW4A16:
                 self.peer_stores = False
             else:
                 from .ops import w4a16_gemm_gather
-                g = self._gen[key]
-                self._gen[key] = g ^ 1
-                buf, ptrs = self._peers[key][g]
+                own = self._owner
+                g = own._gen[key]
+                own._gen[key] = g ^ 1
+                buf, ptrs = own._peers[key][g]
                 w4a16_gemm_gather(A, self.B_local, self.s_local, self.zero, self.group_size, ptrs, self.N, self.n0)
-                dist.all_reduce(self._token, group=self.pg)  # in stream order behind the kernel: all blocks have landed
+                dist.all_reduce(own._token, group=self.pg)  # in stream order behind the kernel: all blocks have landed
                 return buf
         C_local = self._gemm(A, self.B_local, self.s_local, self.zero, self.group_size)
         if not gather or self.world == 1:

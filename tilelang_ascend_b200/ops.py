@@ -353,20 +353,41 @@ def ipc_export(t: torch.Tensor):
     return bytes(handle), int(off.value)
 
 
+_ipc_mappings = {}  # (device index, handle) -> [base address, users]: an allocation is mapped once per process
+
+
 def ipc_open(handle: bytes, device) -> int:
-    """Map a buffer exported by ``ipc_export`` in another process; returns the base address of its allocation."""
+    """Map a buffer exported by ``ipc_export`` in another process; returns the base address of its allocation.
+
+    Several exported buffers can lie in one allocation (torch's allocator carves small tensors out of larger
+    segments) and an allocation can be mapped only once, so mappings are shared and counted."""
     import ctypes
     lib = _lib.load()
+    key = (torch.device(device).index, bytes(handle))
+    hit = _ipc_mappings.get(key)
+    if hit is not None:
+        hit[1] += 1
+        return hit[0]
     buf = (ctypes.c_ubyte * 64).from_buffer_copy(handle)
     base = ctypes.c_void_p(0)
     with torch.cuda.device(device):
         rc = lib.qgemm_ipc_open(ctypes.cast(buf, ctypes.c_void_p), ctypes.cast(ctypes.byref(base), ctypes.c_void_p))
     _lib.check(rc, "qgemm_ipc_open")
+    _ipc_mappings[key] = [int(base.value), 1]
     return int(base.value)
 
 
 def ipc_close(base: int, device):
+    """Drop one use of a mapping made by ``ipc_open``; the last one unmaps the allocation."""
     lib = _lib.load()
+    idx = torch.device(device).index
+    for key, ent in list(_ipc_mappings.items()):
+        if key[0] == idx and ent[0] == base:
+            ent[1] -= 1
+            if ent[1] > 0:
+                return
+            del _ipc_mappings[key]
+            break
     with torch.cuda.device(device):
         _lib.check(lib.qgemm_ipc_close(base), "qgemm_ipc_close")
 
