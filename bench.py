@@ -39,7 +39,7 @@ CFG2 = dict(M=16, K=4096, N=4096, group=128)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the committed ncu
 # summary under profiles/.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 291475712  # profiles/w4a16_gemm_cfg2_headline.md (283.5 MB read + 8.0 MB written)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 295446016  # profiles/w4a16_gs_cfg2_headline.md (283.9 MB read + 11.6 MB written)
 
 
 def w4a16_bytes(M, K, N, group, out_bytes=2, a_bytes=2):
@@ -152,6 +152,8 @@ def timed(fn_step, steps, warmup, world, fn_k_steps=None):
     `fn_k_steps`, when given, issues all K steps at once (one CUDA graph holding K steps)."""
     for _ in range(warmup):
         fn_step()
+    if fn_k_steps is not None:
+        fn_k_steps()  # untimed: the first replay of a graph uploads it to the device
     barrier(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
