@@ -127,14 +127,14 @@ int64_t qgemm_w4a16_counter_bytes(void);
  *   W[n,k]  = scales ? half(q - zero) * scales[k/group, n] : half(q)
  *   C[m,n]  = cast_out( sum_k float(A[m,k]) * float(W[n,k]) )   (fp32 accumulation)
  *
- * Where the scale enters depends on the token count.  Up to 32 tokens (groups of 128, multiples of 256 or
+ * Where the scale enters depends on the token count.  Up to 64 tokens (groups of 128, multiples of 256 or
  * the whole K) the kernels keep (q - zero) exact in f16, accumulate each group in fp32 and multiply the
  * group's sum by its scale in fp32: C = cast_out( sum_g scales[g,n] * sum_{k in g} A[m,k] * (q - zero) ).
  * Above that (and for groups of 32 / 64) every weight is scaled in f16 first, W rounded once as written
  * above.  Both forms give the same result bit for bit when a row of A is one-hot, and differ otherwise by
  * at most the rounding of that f16 product, 2^-11 relative per term; both meet rtol = atol = 1e-2 against
- * the fp32 reference program.  The same inputs may therefore differ in the last bits between, say, M = 32
- * and M = 33.
+ * the fp32 reference program.  The same inputs may therefore differ in the last bits between, say, M = 64
+ * and M = 65.
  *
  * A: [M, K] of a_dtype (F16 / BF16; bf16 is converted to f16 on the fly, as the reference wrapper does,
  *    example_dequant_gemm_fine_grained.py:211-214).  B_packed: [N, K/2] uint8.

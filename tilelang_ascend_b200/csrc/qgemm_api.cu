@@ -98,6 +98,8 @@ int set_smem_w4g() {
   using C = qg::W4GCfg<MT>;
   if (set_smem(qg::w4a16_gs_kernel<MT, false>, C::SMEM_BYTES)) return -1;
   if (set_smem(qg::w4a16_gs_kernel<MT, true>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_gs_kernel<MT, false, true>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_gs_kernel<MT, true, true>, C::SMEM_BYTES)) return -1;
   return 0;
 }
 
@@ -121,7 +123,7 @@ int ensure_device(int* sm_count) {
     }
     if (set_smem_w8<128>() || set_smem_w8<256>()) return -1;
     if (set_smem_w4<16>() || set_smem_w4<32>() || set_smem_w4<64>() || set_smem_w4<128>()) return -1;
-    if (set_smem_w4g<16>() || set_smem_w4g<32>()) return -1;
+    if (set_smem_w4g<16>() || set_smem_w4g<32>() || set_smem_w4g<64>()) return -1;
     if (set_smem_w4i8<16>() || set_smem_w4i8<32>() || set_smem_w4i8<64>() || set_smem_w4i8<128>()) return -1;
     if (set_smem_w4d<0>() || set_smem_w4d<1>() || set_smem_w4d<2>() || set_smem_w4d<4>()) return -1;
     st.sm_count = prop.multiProcessorCount;
@@ -218,11 +220,15 @@ int launch_w4g(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CU
                int grid, cudaStream_t s) {
   qg::W4GDebug dbg;
   dbg.withhold_last_commit = g_w4g_withhold_commit;
+  if (p.n_dst > 0) {
+    if (bf) return launch_pdl(qg::w4a16_gs_kernel<MT, true, true>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
+    return launch_pdl(qg::w4a16_gs_kernel<MT, false, true>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
+  }
   if (bf) return launch_pdl(qg::w4a16_gs_kernel<MT, true>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
   return launch_pdl(qg::w4a16_gs_kernel<MT, false>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
 }
 
-// The group-sum kernel (w4a16_gs.cuh) serves up to 32 tokens when the scale groups are 128 wide, a multiple of
+// The group-sum kernel (w4a16_gs.cuh) serves up to 64 tokens when the scale groups are 128 wide, a multiple of
 // 256 or the whole K (or there are no scales); it is faster than the register-operand decode kernel at every
 // token count (K=8192, N=28672: 36 against 40 us at one token, 37 against 42 us at eight).  Groups of 32 / 64 keep
 // the decode kernel (M <= 8) and the per-weight-scale tcgen05 kernel.  QGEMM_W4_GS=0 disables the group-sum kernel,
@@ -233,7 +239,7 @@ int w4_gs_min_m() {
 }
 bool w4_gs_shape_ok(int64_t M, bool has_scales, int64_t group, int64_t K) {
   static const int enabled = getenv("QGEMM_W4_GS") ? atoi(getenv("QGEMM_W4_GS")) : 1;
-  if (!enabled || M > 32 || M < w4_gs_min_m()) return false;
+  if (!enabled || M > 64 || M < w4_gs_min_m()) return false;
   return !has_scales || group == 128 || group % 256 == 0 || group >= K;
 }
 
@@ -263,7 +269,7 @@ bool w4_use_decode(int64_t M) { return M <= w4_decode_max_m(); }
 // Token-tile height: 8 for the decode kernel, 16..128 for the tcgen05 kernel.
 // Token-tile height: 16 / 32 for the group-sum kernel, 8 for the decode kernel, 16..128 for the tcgen05 kernel.
 int w4_pick_mt(int64_t M, bool gs) {
-  if (gs) return M <= 16 ? 16 : 32;
+  if (gs) return M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   if (w4_use_decode(M)) return M <= 8 ? 8 : 16;
   return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
 }
@@ -558,7 +564,7 @@ static int64_t w4_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K
   if (ensure_device(&sms)) return -1;
   const int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
   // sized for whichever small-token kernel the scale groups will select (the group-sum kernel's tile is the taller)
-  const int mt = M <= 32 ? w4_pick_mt(M, true) : w4_pick_mt(M, false);
+  const int mt = M <= 64 ? w4_pick_mt(M, true) : w4_pick_mt(M, false);
   // the arrival counters first (fixed place whatever the tile height), then two partial slots of
   // [MT][128] fp32 per CTA, then the f16 copy of the activations in the kernel's K order
   // ... and, for the large-token path, the dequantised f16 weights
@@ -827,7 +833,8 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
   }
   if (use_gs) {
     if (mt == 16) return launch_w4g<16>(bf, tmW, tmS, tmA, p, (int)grid, s);
-    return launch_w4g<32>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    if (mt == 32) return launch_w4g<32>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    return launch_w4g<64>(bf, tmW, tmS, tmA, p, (int)grid, s);
   }
   if (gd == nullptr && w4_use_decode(M) && mt <= 16 && M <= w4_decode_max_m()) {
     if (scales == nullptr) return launch_w4d<0>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);

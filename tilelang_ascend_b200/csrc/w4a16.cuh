@@ -99,15 +99,18 @@ __device__ __forceinline__ void w4_tile_coords(const W4A16Params& p, int tile, i
   m0 = (t % p.m_tiles) * mt;
 }
 
-// One output value C[b][m][n] (or, in the gathered form, column col0 + n of row m of every destination).
-template <bool OUT_BF16>
+// One output value C[b][m][n] or, in the gathered form, column col0 + n of row m of every destination.
+template <bool OUT_BF16, bool GATHER = true>
 __device__ __forceinline__ void w4_store_out(const W4A16Params& p, uint16_t* Cout, int m, int n, float v) {
   const uint16_t h = OUT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
-  if (p.n_dst == 0) {
+  if (!GATHER || p.n_dst == 0) {
     Cout[(size_t)m * p.N + n] = h;
   } else {
     const size_t off = (size_t)m * p.ldc + p.col0 + n;
-    for (int d = 0; d < p.n_dst; ++d) reinterpret_cast<uint16_t*>(p.c_dst[d])[off] = h;
+    // constant indices only: a run-time index into the kernel's parameter block would move it to local memory
+#pragma unroll
+    for (int d = 0; d < 8; ++d)
+      if (d < p.n_dst) reinterpret_cast<uint16_t*>(p.c_dst[d])[off] = h;
   }
 }
 

@@ -1,4 +1,4 @@
-// W4A16 dequantize-GEMM for up to 32 tokens (the memory-bound decode regime), group-sum form, sm_100a:
+// W4A16 dequantize-GEMM for up to 64 tokens (the memory-bound decode regime), group-sum form, sm_100a:
 //   C[m, n] = cast( sum_g s[g, n] * ( sum_{k in g} float(A[m, k]) * (q[n, k] - zero) ) )
 // i.e. the group scale multiplies the group's fp32 partial sum instead of every weight.  With one-hot
 // activations this equals half(q - zero) * s bit for bit (the fp32 product of two f16 values is exact
@@ -79,14 +79,18 @@ constexpr int W4G_EPI_CTRL = 856;     // u32[2], alternating by segment: bit 0 a
 
 template <int MT>
 struct W4GCfg {
-  static_assert(MT == 16 || MT == 32, "token tile");
-  static constexpr int AS = (MT == 16) ? 8 : 4;    // activation ring (even: an issuer meets every phase of its stages)
-  static constexpr int NSLOT = 128 / MT;           // slab slots of two accumulators each (8 or 4)
+  static_assert(MT == 16 || MT == 32 || MT == 64, "token tile");
+  static constexpr int AS = (MT == 16) ? 8 : (MT == 32 ? 4 : 2);  // activation ring (even: an issuer meets every phase of its stages)
+  static constexpr int NSLOT = 128 / MT;           // slab slots of two accumulators each (8, 4 or 2)
+  // How the two drain sets share the work: on alternate slabs, all tokens each (their sums meet at a segment's
+  // end), or - 64 tokens would not fit a thread's registers - every slab, 32 tokens each (nothing to exchange).
+  static constexpr bool SPLIT_TOKENS = MT == 64;
+  static constexpr int DT = SPLIT_TOKENS ? 32 : MT;  // tokens one drain thread accumulates
   static constexpr int A_KB_BYTES = MT * 128;      // one 64-wide K block of activations
   static constexpr int A_BYTES = 4 * A_KB_BYTES;   // one 256-wide slab
   static constexpr int TMEM_COLS = 512;
   static constexpr int BAR_BYTES = 1024;
-  static constexpr int XBUF_BYTES = MT * W4_BN * 4;  // the second drain set's sums of one segment
+  static constexpr int XBUF_BYTES = SPLIT_TOKENS ? 0 : MT * W4_BN * 4;  // the second drain set's sums of one segment
   static constexpr int SMEM_BYTES =
       W4G_RS * W4_RAW_PACKED + AS * A_BYTES + W4G_SS * W4G_SC_BYTES + XBUF_BYTES + BAR_BYTES + 1024;
   static constexpr int A_PER = AS / 2;                // activation stages one issuer meets
@@ -167,7 +171,10 @@ __device__ __forceinline__ uint32_t w4g_visit_parity(uint32_t c, int u) {
   return (PER == 4) ? (c & 1u) : (uint32_t)((u / PER) & 1);
 }
 
-template <int MT, bool OUT_BF16>
+// GATHER = true is the gathered form (several destination buffers, see W4A16Params::c_dst); it is a separate
+// instantiation because the destination loop in the store path costs the plain kernel 8 % through register
+// allocation alone.
+template <int MT, bool OUT_BF16, bool GATHER = false>
 __global__ void __launch_bounds__(W4G_THREADS, 1)
 w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
                 const __grid_constant__ CUtensorMap tmA, const W4A16Params p, const W4GDebug dbg) {
@@ -219,11 +226,11 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     }
     for (int i = 0; i < NSLOT; ++i) {
       mbar_init(&acc_full[i], 2);   // the issuers of the slab's two halves
-      mbar_init(&acc_empty[i], 4);  // the four drain warps of the set that took the slab
+      mbar_init(&acc_empty[i], Cfg::SPLIT_TOKENS ? 8 : 4);  // the drain warps that read the slab: one set, or both
     }
     for (int s = 0; s < SS; ++s) {
       mbar_init(&sc_full[s], 1);
-      mbar_init(&sc_empty[s], 4);
+      mbar_init(&sc_empty[s], Cfg::SPLIT_TOKENS ? 8 : 4);
     }
     mbar_init(drain, W4G_MMA_WARPS);
     ctl_words[0] = 0;
@@ -396,10 +403,13 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       const bool full_tile = (ks0 == 0 && ks1 == p.KS);
       const int my_slot = (ks1 < p.KS) ? 2 * cta + 1 : 2 * cta;
       const uint32_t i_end = i_seg0 + (uint32_t)(ks1 - ks0);
-      float psum[MT];
+      constexpr int DT = Cfg::DT;
+      constexpr bool SPLIT_TOKENS = Cfg::SPLIT_TOKENS;
+      const int tok0 = SPLIT_TOKENS ? 32 * e : 0;  // first token (inside the tile) of this thread's sums
+      float psum[DT];
 #pragma unroll
-      for (int m = 0; m < MT; ++m) psum[m] = 0.f;
-      for (uint32_t i = i_seg0 + ((i_seg0 ^ (uint32_t)e) & 1u); i < i_end; i += 2) {
+      for (int m = 0; m < DT; ++m) psum[m] = 0.f;
+      for (uint32_t i = SPLIT_TOKENS ? i_seg0 : i_seg0 + ((i_seg0 ^ (uint32_t)e) & 1u); i < i_end; i += SPLIT_TOKENS ? 1 : 2) {
         float s0 = 1.0f, s1 = 1.0f;
         if (scaled) {
           const uint32_t ss = i % SS;
@@ -416,7 +426,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         const uint32_t bs = bar0 + 8 * slot;
         w4g_wait<W4G_ACC_FULL, ST_TIMEOUT_EPILOGUE>(bs, (i / NSLOT) & 1u, ctl, fail);
         tc_fence_after_sync();
-        const uint32_t ta = tmem_base + lane_addr + slot * (2 * MT);
+        const uint32_t ta = tmem_base + lane_addr + slot * (2 * MT) + tok0;
         if constexpr (MT == 16) {
           uint32_t r[32];  // columns 0..15: first half's accumulator, 16..31: second half's
           tmem_ld_32x32b_x32(ta, r);
@@ -431,9 +441,9 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           }
         } else {
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {  // 16 columns at a time: half c4 / 2, tokens 16 * (c4 % 2) ..
+          for (int c4 = 0; c4 < 4; ++c4) {  // 16 columns at a time: half c4 / 2, this thread's tokens 16 * (c4 % 2) ..
             uint32_t r[16];
-            tmem_ld_32x32b_x16(ta + 16 * c4, r);
+            tmem_ld_32x32b_x16(ta + (c4 >> 1) * MT + 16 * (c4 & 1), r);
             tmem_ld_wait();
             if (c4 == 3) {
               tc_fence_before_sync();
@@ -448,14 +458,15 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       }
       i_seg0 = i_end;
       fail = __any_sync(0xffffffffu, fail != 0) ? 1u : 0u;
-      // Segment end.  Set 1 hands over its sums (set 0 has read them before it reaches the second barrier below,
-      // which set 1 passes before its next hand-over); set 0 adds them and writes the tile or its split-K partial.
+      // Segment end.  With slab-alternating sets, set 1 hands over its sums (set 0 has read them before it reaches
+      // the second barrier below, which set 1 passes before its next hand-over) and set 0 adds them and writes the
+      // tile or its split-K partial; with token-split sets each set writes its own tokens.
       const int par = seg_idx & 1;
       ++seg_idx;
       float* xb = xbuf + nl;
-      if (e == 1) {
+      if (!SPLIT_TOKENS && e == 1) {
 #pragma unroll
-        for (int j = 0; j < MT; ++j) xb[j * W4_BN] = psum[j];
+        for (int j = 0; j < DT; ++j) xb[j * W4_BN] = psum[j];
       }
       w4g_epi_bar();
       const long long first_item = (long long)tile * p.KS;
@@ -464,22 +475,23 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         b_first = w4_owner(T, G, first_item);
         b_last = w4_owner(T, G, first_item + p.KS - 1);
       }
-      if (e == 0 && !fail) {
+      if ((SPLIT_TOKENS || e == 0) && !fail) {
+        if (!SPLIT_TOKENS) {
 #pragma unroll
-        for (int j = 0; j < MT; ++j) psum[j] += xb[j * W4_BN];
+          for (int j = 0; j < DT; ++j) psum[j] += xb[j * W4_BN];
+        }
         if (full_tile) {
           if (n < p.N) {
 #pragma unroll
-            for (int j = 0; j < MT; ++j) {
-              const int m = m0 + j;
-              if (m < p.M)
-                w4_store_out<OUT_BF16>(p, Cout, m, n, psum[j]);
+            for (int j = 0; j < DT; ++j) {
+              const int m = m0 + tok0 + j;
+              if (m < p.M) w4_store_out<OUT_BF16, GATHER>(p, Cout, m, n, psum[j]);
             }
           }
         } else {
-          float* dst = p.ws_partials + (size_t)my_slot * (MT * W4_BN) + nl;
+          float* dst = p.ws_partials + (size_t)my_slot * (MT * W4_BN) + (size_t)tok0 * W4_BN + nl;
 #pragma unroll
-          for (int j = 0; j < MT; ++j) dst[j * W4_BN] = psum[j];
+          for (int j = 0; j < DT; ++j) dst[j * W4_BN] = psum[j];
           __threadfence();
         }
       }
@@ -500,12 +512,12 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       const uint32_t ctrl = epi_ctrl[par];
       if (ctrl & 1u) break;
       const bool is_last = (ctrl & 2u) != 0;
-      if (is_last && e == 0) {
+      if (is_last && (Cfg::SPLIT_TOKENS || e == 0)) {
         __threadfence();
         if (n < p.N) {
-          const int rows = min(MT, p.M - m0);
+          const int rows = min(Cfg::SPLIT_TOKENS ? 32 * e + 32 : MT, p.M - m0);
 #pragma unroll 1
-          for (int mb = 0; mb < rows; mb += 16) {
+          for (int mb = Cfg::SPLIT_TOKENS ? 32 * e : 0; mb < rows; mb += 16) {
             float sum[16];
 #pragma unroll
             for (int u = 0; u < 16; ++u) sum[u] = 0.0f;
@@ -523,7 +535,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 #pragma unroll
             for (int u = 0; u < 16; ++u) {
               if (mb + u < rows)
-                w4_store_out<OUT_BF16>(p, Cout, m0 + mb + u, n, sum[u]);
+                w4_store_out<OUT_BF16, GATHER>(p, Cout, m0 + mb + u, n, sum[u]);
             }
           }
         }
