@@ -211,33 +211,31 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
 
+  // One thread per barrier slot sets it up (the block is a dense array of 8-byte slots; a serial loop over the
+  // hundred of them costs about a microsecond of every launch).
+  if (threadIdx.x <= W4G_DRAIN / 8) {
+    const int off = 8 * (int)threadIdx.x;
+    const int drain_warps = Cfg::SPLIT_TOKENS ? 8 : 4;  // drain warps that read one slab: one set, or both
+    int count = 0;                                       // 0: unused slot
+    if (off < W4G_RAW_EMPTY) count = 1;
+    else if (off < W4G_A_FULL) count = W4G_DQ_WARPS / 2;   // the eight dequant warps of the set that took the slab
+    else if (off < W4G_A_EMPTY) count = (off - W4G_A_FULL) / 8 < AS ? 1 : 0;
+    else if (off < W4G_W_FULL) count = (off - W4G_A_EMPTY) / 8 < AS ? 2 : 0;  // the issuers of the slab's two halves
+    else if (off < W4G_W_EMPTY) count = 4;                 // the four dequant warps (one per 32 rows) of that half
+    else if (off < W4G_ACC_FULL) count = 1;
+    else if (off < W4G_ACC_EMPTY) count = (off - W4G_ACC_FULL) / 8 < NSLOT ? 2 : 0;  // the issuers of the two halves
+    else if (off < W4G_SC_FULL) count = (off - W4G_ACC_EMPTY) / 8 < NSLOT ? drain_warps : 0;
+    else if (off < W4G_SC_EMPTY) count = 1;
+    else if (off < W4G_DRAIN) count = drain_warps;
+    else count = W4G_MMA_WARPS;
+    if (count > 0) mbar_init(reinterpret_cast<uint64_t*>(bar_block + off), (uint32_t)count);
+    fence_barrier_init();
+  }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < RS; ++s) {
-      mbar_init(&raw_full[s], 1);
-      mbar_init(&raw_empty[s], W4G_DQ_WARPS / 2);  // the eight dequant warps of the set that took the slab
-    }
-    for (int s = 0; s < AS; ++s) {
-      mbar_init(&a_full[s], 1);
-      mbar_init(&a_empty[s], 2);  // the issuers of the slab's two halves
-    }
-    for (int s = 0; s < W4G_WH; ++s) {
-      mbar_init(&w_full[s], 4);  // the four dequant warps (one per 32 rows) of that half
-      mbar_init(&w_empty[s], 1);
-    }
-    for (int i = 0; i < NSLOT; ++i) {
-      mbar_init(&acc_full[i], 2);   // the issuers of the slab's two halves
-      mbar_init(&acc_empty[i], Cfg::SPLIT_TOKENS ? 8 : 4);  // the drain warps that read the slab: one set, or both
-    }
-    for (int s = 0; s < SS; ++s) {
-      mbar_init(&sc_full[s], 1);
-      mbar_init(&sc_empty[s], Cfg::SPLIT_TOKENS ? 8 : 4);
-    }
-    mbar_init(drain, W4G_MMA_WARPS);
     ctl_words[0] = 0;
     // a failed try_wait has suspended the thread for roughly 2 us or longer
     ctl_words[1] = (uint32_t)(p.wait_limit_ns >> 11) + 2u;
     epi_ctrl[0] = epi_ctrl[1] = 0;
-    fence_barrier_init();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmA);
     if (p.has_scales) tma_prefetch_desc(&tmS);
