@@ -373,3 +373,50 @@ def test_bounded_wait_expires_cleanly_and_the_next_call_is_exact():
     assert int(status.item()) == 0
     C2 = q.w4a16_gemm(Ad, Pd, Sd, 8, 128, check_status=True)
     assert torch.equal(C, C2)
+
+
+def test_back_to_back_calls_that_feed_each_other():
+    """Calls issued back to back overlap: a call's pre-pass is resident and its GEMM kernel is already streaming
+    weights while the call in front still runs.  Here every call reads the previous call's output as its
+    activations and all calls share one scratch area (the built-in one), so any step taken too early shows: the
+    chain must be bit-identical to the same chain with the device drained between calls, and match the oracle."""
+    from tilelang_ascend_b200 import _lib
+    lib = _lib.load()
+    M, K, layers = 16, 2048, 6
+    g = torch.Generator().manual_seed(77)
+    A0, _, _ = oc.make_w4a16_inputs(M, K, K, "float16", 128, seed=70)
+    Ws = []
+    for l in range(layers):
+        _, P, S = oc.make_w4a16_inputs(M, K, K, "float16", 128, seed=71 + l)
+        # keep the chain's magnitude steady: rescale so that one layer maps unit-variance rows to about unit variance
+        W = oc.dequant_weight_ref(P, S, 8, 128).float()
+        gain = (torch.randn(64, K, generator=g) @ W.t()).std().item()
+        Ws.append((P, (S.float() / gain).to(torch.float16)))
+    dev = [(P.cuda(), S.cuda()) for P, S in Ws]
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def chain(drain):
+        x = A0.cuda()
+        outs = []
+        for P, S in dev:
+            C = torch.empty((M, K), dtype=torch.float16, device="cuda")
+            rc = lib.qgemm_w4a16_noalloc(x.data_ptr(), P.data_ptr(), S.data_ptr(), 8, 128, C.data_ptr(), M, K, K,
+                                         _lib.DT_F16, _lib.DT_F16, None, stream)
+            assert rc == 0, _lib.last_error()
+            if drain:
+                torch.cuda.synchronize()
+            outs.append(C)
+            x = C
+        torch.cuda.synchronize()
+        return outs
+
+    want = chain(drain=True)
+    for _ in range(3):
+        got = chain(drain=False)
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+    x = A0
+    for (P, S), c in zip(Ws, want):
+        ref = oc.dequant_gemm_fp16_ref(x, P, "float16", S, 8, 128)
+        _close(c, ref)
+        x = c.cpu()

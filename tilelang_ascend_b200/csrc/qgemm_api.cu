@@ -100,6 +100,8 @@ int set_smem_w4g() {
   if (set_smem(qg::w4a16_gs_kernel<MT, true>, C::SMEM_BYTES)) return -1;
   if (set_smem(qg::w4a16_gs_kernel<MT, false, true>, C::SMEM_BYTES)) return -1;
   if (set_smem(qg::w4a16_gs_kernel<MT, true, true>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_gs_kernel<MT, false, false, true>, C::SMEM_BYTES)) return -1;
+  if (set_smem(qg::w4a16_gs_kernel<MT, true, false, true>, C::SMEM_BYTES)) return -1;
   return 0;
 }
 
@@ -215,17 +217,23 @@ int launch_w4(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUt
 // Test hook (qgemm_debug_withhold_commit): see W4GDebug.
 int g_w4g_withhold_commit = 0;
 
+// `tmZ` non-null: the zeros-tensor instantiation (not combined with the gathered form).
 template <int MT>
-int launch_w4g(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA, const qg::W4A16Params& p,
-               int grid, cudaStream_t s) {
+int launch_w4g(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap* tmZ, const CUtensorMap& tmA,
+               const qg::W4A16Params& p, int grid, cudaStream_t s) {
   qg::W4GDebug dbg;
   dbg.withhold_last_commit = g_w4g_withhold_commit;
-  if (p.n_dst > 0) {
-    if (bf) return launch_pdl(qg::w4a16_gs_kernel<MT, true, true>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
-    return launch_pdl(qg::w4a16_gs_kernel<MT, false, true>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
+  constexpr int smem = qg::W4GCfg<MT>::SMEM_BYTES;
+  if (tmZ != nullptr) {
+    if (bf) return launch_pdl(qg::w4a16_gs_kernel<MT, true, false, true>, grid, qg::W4G_THREADS, smem, s, tmW, tmS, *tmZ, tmA, p, dbg);
+    return launch_pdl(qg::w4a16_gs_kernel<MT, false, false, true>, grid, qg::W4G_THREADS, smem, s, tmW, tmS, *tmZ, tmA, p, dbg);
   }
-  if (bf) return launch_pdl(qg::w4a16_gs_kernel<MT, true>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
-  return launch_pdl(qg::w4a16_gs_kernel<MT, false>, grid, qg::W4G_THREADS, qg::W4GCfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p, dbg);
+  if (p.n_dst > 0) {
+    if (bf) return launch_pdl(qg::w4a16_gs_kernel<MT, true, true>, grid, qg::W4G_THREADS, smem, s, tmW, tmS, tmS, tmA, p, dbg);
+    return launch_pdl(qg::w4a16_gs_kernel<MT, false, true>, grid, qg::W4G_THREADS, smem, s, tmW, tmS, tmS, tmA, p, dbg);
+  }
+  if (bf) return launch_pdl(qg::w4a16_gs_kernel<MT, true>, grid, qg::W4G_THREADS, smem, s, tmW, tmS, tmS, tmA, p, dbg);
+  return launch_pdl(qg::w4a16_gs_kernel<MT, false>, grid, qg::W4G_THREADS, smem, s, tmW, tmS, tmS, tmA, p, dbg);
 }
 
 // The group-sum kernel (w4a16_gs.cuh) serves up to 64 tokens when the scale groups are 128 wide, a multiple of
@@ -723,7 +731,13 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     zero = 0;
     group = K;
   }
-  const bool dequant_once = zeros != nullptr || w4_use_f16_gemm(M, N);
+  // A zeros tensor of mode "quantized" (integer zero points) is taken in flight by the group-sum kernel wherever that
+  // kernel applies; the other zero modes, whose f16 roundings per weight the group-sum form cannot reproduce, and all
+  // other shapes go through the whole-matrix dequantisation.  QGEMM_W4_ZEROS_INFLIGHT=0 sends every zeros tensor there.
+  static const int zeros_inflight_on = getenv("QGEMM_W4_ZEROS_INFLIGHT") ? atoi(getenv("QGEMM_W4_ZEROS_INFLIGHT")) : 1;
+  const bool zeros_inflight = zeros != nullptr && zeros_inflight_on && zero_mode == QGEMM_ZERO_QUANTIZED && gd == nullptr &&
+                              !w4_use_f16_gemm(M, N) && w4_gs_shape_ok(M, true, group, K);
+  const bool dequant_once = (zeros != nullptr && !zeros_inflight) || w4_use_f16_gemm(M, N);
   const int64_t need = w4_workspace_bytes(batch, M, N, K, zeros != nullptr);
   if (need < 0) return -1;
   if (workspace == nullptr || workspace_bytes < need) return fail("qgemm_w4a16: workspace of %lld bytes needed (got %lld)", (long long)need, (long long)workspace_bytes);
@@ -734,8 +748,9 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
   int mt = w4_pick_mt(M, use_gs);
   if (gd != nullptr && mt < 16) mt = 16;  // the register-operand decode kernel writes one destination only
 
-  CUtensorMap tmW, tmS, tmA;
+  CUtensorMap tmW, tmS, tmZ, tmA;
   memset(&tmS, 0, sizeof(tmS));
+  memset(&tmZ, 0, sizeof(tmZ));
   {
     const uint64_t dims[3] = {(uint64_t)(K / 2), (uint64_t)N, (uint64_t)batch};
     const uint64_t str[2] = {(uint64_t)(K / 2), (uint64_t)N * (uint64_t)(K / 2)};
@@ -750,6 +765,9 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     const uint64_t str[2] = {(uint64_t)N * 2, (uint64_t)(K / group) * (uint64_t)N * 2};
     const uint32_t box[3] = {128, (uint32_t)scale_rows, 1};
     if (encode_map(&tmS, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, scales, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return -1;
+    if (zeros_inflight &&
+        encode_map(&tmZ, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, zeros, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return -1;
   }
   const int64_t grid_max = sms < kW4MaxGrid ? sms : kW4MaxGrid;
   uint8_t* a_prepared = static_cast<uint8_t*>(workspace) + kW4CounterBytes + grid_max * 2 * (int64_t)mt * 128 * 4;
@@ -810,12 +828,23 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     const long long n_chunks = (long long)batch * M * K / 8;
     const long long blocks = (n_chunks + 255) / 256;
     if (blocks > 0x7fffffffll) return fail("qgemm_w4a16: activation tensor too large");
-    qg::w4a16_prepare_activations<<<(unsigned)blocks, 256, 0, s>>>(static_cast<const uint4*>(A),
-                                                                  reinterpret_cast<uint4*>(a_prepared), n_chunks,
-                                                                  a_dtype == QGEMM_DT_BF16 ? 1 : 0,
-                                                                  weight_format == QGEMM_W4_SEQUENTIAL ? 1 : 0,
-                                                                  p.ws_counters, (int)(kW4CounterBytes / 4));
-    CUDA_OK(cudaGetLastError());
+    // Launched as a programmatic dependent too: behind another call of this operator (whose GEMM kernel lets its
+    // dependents go at once) the pre-pass is already resident, waiting, when that call ends, and the GEMM kernel
+    // behind it sets up and streams its first weights meanwhile.  Behind any other kernel this is plain stream order.
+    static const int chain = getenv("QGEMM_PDL_CHAIN") ? atoi(getenv("QGEMM_PDL_CHAIN")) : 1;
+    const uint4* a_in = static_cast<const uint4*>(A);
+    uint4* a_out = reinterpret_cast<uint4*>(a_prepared);
+    const int is_bf = a_dtype == QGEMM_DT_BF16 ? 1 : 0, permute = weight_format == QGEMM_W4_SEQUENTIAL ? 1 : 0;
+    const int n_counters = (int)(kW4CounterBytes / 4);
+    if (chain) {
+      if (launch_pdl(qg::w4a16_prepare_activations, (int)blocks, 256, 0, s, a_in, a_out, n_chunks, is_bf, permute,
+                     p.ws_counters, n_counters))
+        return -1;
+    } else {
+      qg::w4a16_prepare_activations<<<(unsigned)blocks, 256, 0, s>>>(a_in, a_out, n_chunks, is_bf, permute,
+                                                                    p.ws_counters, n_counters);
+      CUDA_OK(cudaGetLastError());
+    }
   }
   if (dequant_once) {
     uint8_t* w16 = a_prepared + batch * M * K * 2;
@@ -832,9 +861,10 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     return w4_f16_gemm(a_prepared, w16, C, batch, M, N, K, bf, status, s, sms, gd);
   }
   if (use_gs) {
-    if (mt == 16) return launch_w4g<16>(bf, tmW, tmS, tmA, p, (int)grid, s);
-    if (mt == 32) return launch_w4g<32>(bf, tmW, tmS, tmA, p, (int)grid, s);
-    return launch_w4g<64>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    const CUtensorMap* tz = zeros_inflight ? &tmZ : nullptr;
+    if (mt == 16) return launch_w4g<16>(bf, tmW, tmS, tz, tmA, p, (int)grid, s);
+    if (mt == 32) return launch_w4g<32>(bf, tmW, tmS, tz, tmA, p, (int)grid, s);
+    return launch_w4g<64>(bf, tmW, tmS, tz, tmA, p, (int)grid, s);
   }
   if (gd == nullptr && w4_use_decode(M) && mt <= 16 && M <= w4_decode_max_m()) {
     if (scales == nullptr) return launch_w4d<0>(bf, mt, tmW, tmS, tmA, p, (int)grid, s);

@@ -234,6 +234,7 @@ __global__ void __launch_bounds__(256)
 w4a16_prepare_activations(const uint4* __restrict__ in, uint4* __restrict__ out, long long n_chunks, int is_bf16,
                           int permute, uint32_t* __restrict__ counters, int n_counters) {
   pdl_launch_dependents();  // the GEMM kernel behind may set up and start streaming weights meanwhile
+  pdl_wait();               // the kernel in front (another call's GEMM, which lets its dependents start early) is done
   if (blockIdx.x == 0)
     for (int c = threadIdx.x; c < n_counters; c += blockDim.x) counters[c] = 0u;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;

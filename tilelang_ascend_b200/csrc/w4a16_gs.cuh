@@ -92,7 +92,7 @@ struct W4GCfg {
   static constexpr int BAR_BYTES = 1024;
   static constexpr int XBUF_BYTES = SPLIT_TOKENS ? 0 : MT * W4_BN * 4;  // the second drain set's sums of one segment
   static constexpr int SMEM_BYTES =
-      W4G_RS * W4_RAW_PACKED + AS * A_BYTES + W4G_SS * W4G_SC_BYTES + XBUF_BYTES + BAR_BYTES + 1024;
+      W4G_RS * W4_RAW_PACKED + AS * A_BYTES + W4G_SS * W4G_SC_BYTES + W4G_RS * W4G_SC_BYTES + XBUF_BYTES + BAR_BYTES + 1024;
   static constexpr int A_PER = AS / 2;                // activation stages one issuer meets
   static constexpr int S_PER = NSLOT / 2;             // slab slots one issuer meets (those of its slab parity)
   static_assert(A_PER == 4 || A_PER == 2 || A_PER == 1, "activation ring depth");
@@ -174,24 +174,34 @@ __device__ __forceinline__ uint32_t w4g_visit_parity(uint32_t c, int u) {
 // GATHER = true is the gathered form (several destination buffers, see W4A16Params::c_dst); it is a separate
 // instantiation because the destination loop in the store path costs the plain kernel 8 % through register
 // allocation alone.
-template <int MT, bool OUT_BF16, bool GATHER = false>
+// ZT = true: one integer zero point per (group, output feature) instead of the scalar one - the zeros tensor
+// [K/g, N] f16 of zero mode "quantized" (tilelang/quantize/lop3.py:325-358: (q - qz) * s with the subtraction
+// exact).  The weight producer fetches the slab's zero rows (through tmZ, laid out like the scale rows) into a ring
+// that shares the packed weights' stages and barriers, and a dequant thread builds its row's two magic constants
+// from the zero it reads there: five more instructions per 128-k half.
+template <int MT, bool OUT_BF16, bool GATHER = false, bool ZT = false>
 __global__ void __launch_bounds__(W4G_THREADS, 1)
 w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
-                const __grid_constant__ CUtensorMap tmA, const W4A16Params p, const W4GDebug dbg) {
+                const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmA, const W4A16Params p,
+                const W4GDebug dbg) {
   using Cfg = W4GCfg<MT>;
   constexpr int RS = W4G_RS;
   constexpr int AS = Cfg::AS;
   constexpr int NSLOT = Cfg::NSLOT;
   constexpr int SS = W4G_SS;
   static_assert(RS == 8 && SS == 16 && AS <= 8 && NSLOT <= 8, "barrier block layout");
+  // The next call's pre-pass (a programmatic dependent) may become resident now; it waits for this whole grid before
+  // it touches anything, and the GEMM kernel behind it only reads weights and scales until that pre-pass is done.
+  pdl_launch_dependents();
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* raw_base = smem;
   uint8_t* a_base = smem + RS * W4_RAW_PACKED;
   uint8_t* sc_base = a_base + AS * Cfg::A_BYTES;
-  float* xbuf = reinterpret_cast<float*>(sc_base + SS * W4G_SC_BYTES);
-  uint8_t* bar_block = sc_base + SS * W4G_SC_BYTES + Cfg::XBUF_BYTES;
+  uint8_t* z_base = sc_base + SS * W4G_SC_BYTES;  // zero rows, one 512-byte stage per raw stage (ZT only)
+  float* xbuf = reinterpret_cast<float*>(z_base + RS * W4G_SC_BYTES);
+  uint8_t* bar_block = z_base + RS * W4G_SC_BYTES + Cfg::XBUF_BYTES;
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(bar_block + W4G_RAW_FULL);
   uint64_t* raw_empty = reinterpret_cast<uint64_t*>(bar_block + W4G_RAW_EMPTY);
   uint64_t* a_full = reinterpret_cast<uint64_t*>(bar_block + W4G_A_FULL);
@@ -239,6 +249,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmA);
     if (p.has_scales) tma_prefetch_desc(&tmS);
+    if (ZT) tma_prefetch_desc(&tmZ);
   }
   if (warp == 2) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -277,8 +288,12 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         w4g_wait<0, ST_TIMEOUT_PRODUCER>(empty0 + 8 * st, phase ^ 1u, ctl, fail);
         if (fail) break;
         if (warp == 0) {
-          mbar_arrive_expect_tx(&full[st], W4_RAW_PACKED);
+          mbar_arrive_expect_tx(&full[st], ZT ? W4_RAW_PACKED + sc_tx : (uint32_t)W4_RAW_PACKED);
           tma_load_3d(raw_base + st * W4_RAW_PACKED, &tmW, &full[st], ks * (W4_SLAB_K / 2), n0, b);
+          if (ZT) {  // the zero rows of the slab's two halves, addressed like its scale rows
+            const int zrow = (p.scale_rows == 2) ? 2 * ks : (ks * W4_SLAB_K) / p.group;
+            tma_load_3d(z_base + st * W4G_SC_BYTES, &tmZ, &full[st], n0, zrow, b);
+          }
         } else if (warp == 1) {
           uint8_t* dstA = a_base + st * Cfg::A_BYTES;
           mbar_arrive_expect_tx(&full[st], Cfg::A_BYTES);
@@ -557,8 +572,10 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     const uint32_t ch0 = rawr + (((4 * hf + 0) ^ sw) << 4), ch1 = rawr + (((4 * hf + 1) ^ sw) << 4);
     const uint32_t ch2 = rawr + (((4 * hf + 2) ^ sw) << 4), ch3 = rawr + (((4 * hf + 3) ^ sw) << 4);
     const uint32_t zero = (uint32_t)p.zero;
-    const uint32_t sub_lo = (0x6400u + zero) * 0x00010001u;                     // (1024 + zero) x2
-    const uint32_t sub_hi = ((0x5400u + (zero << 4)) | 0x8000u) * 0x00010001u;  // -(64 + zero) x2
+    const uint32_t sub_lo_c = (0x6400u + zero) * 0x00010001u;                     // (1024 + zero) x2
+    const uint32_t sub_hi_c = ((0x5400u + (zero << 4)) | 0x8000u) * 0x00010001u;  // -(64 + zero) x2
+    // this row's zero point of the half: stage g of the zero ring, second row for the second half of 128-wide groups
+    const uint32_t z_addr = smem_u32(z_base) + g * W4G_SC_BYTES + 2 * row + ((p.scale_rows == 2 && hf) ? 256u : 0u);
     const uint32_t st_addr = tmem_w + ((uint32_t)(q * 32) << 16) + (2 * g + hf) * W4G_HALF_COLS;
     const uint32_t bg = bar0 + 8 * g;             // raw stages g, g + 2, g + 4, g + 6
     const uint32_t bws = bar0 + 8 * (2 * g + hf);  // weight stage 2 g + hf
@@ -571,6 +588,17 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         constexpr int u = decltype(u_)::value;
         if (nb + u >= n_mine) return;
         w4g_wait<W4G_RAW_FULL + 16 * u, ST_TIMEOUT_DEQUANT>(bg, rphase, ctl, fail);
+        uint32_t sub_lo = sub_lo_c, sub_hi = sub_hi_c;
+        if constexpr (ZT) {
+          // integer zero z as f16: 1024 + z and 64 + z are exact f16 sums
+          uint16_t zh;
+          asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(zh) : "r"(z_addr), "n"(2 * u * W4G_SC_BYTES));
+          uint32_t z2;
+          asm("mov.b32 %0, {%1, %1};" : "=r"(z2) : "h"(zh));
+          asm("add.rn.f16x2 %0, %1, %2;" : "=r"(sub_lo) : "r"(0x64006400u), "r"(z2));
+          asm("add.rn.f16x2 %0, %1, %2;" : "=r"(sub_hi) : "r"(0x54005400u), "r"(z2));
+          sub_hi ^= 0x80008000u;
+        }
         const uint4 v0 = w4g_lds128<2 * u * W4_RAW_PACKED>(ch0);
         const uint4 v1 = w4g_lds128<2 * u * W4_RAW_PACKED>(ch1);
         const uint4 v2 = w4g_lds128<2 * u * W4_RAW_PACKED>(ch2);
