@@ -377,11 +377,11 @@ static int w4a8_fused(const int8_t* A, const uint8_t* qB, int8_t* workspace, int
   p.status = status;
   p.wait_limit_ns = g_wait_limit_ns;
   int64_t grid = grid_max < p.total_items ? grid_max : p.total_items;
-  qg::w4a8_prepare_activations<<<(unsigned)M, 256, 0, s>>>(reinterpret_cast<const uint2*>(A),
-                                                          reinterpret_cast<uint2*>(a_prepared), row_sums,
-                                                          reinterpret_cast<uint32_t*>(ws), (int)(kW4CounterBytes / 4),
-                                                          (int)K);
-  CUDA_OK(cudaGetLastError());
+  // a programmatic dependent of whatever is in front: behind another call of this operator it is resident early
+  if (launch_pdl(qg::w4a8_prepare_activations, (int)M, 256, 0, s, reinterpret_cast<const uint2*>(A),
+                 reinterpret_cast<uint2*>(a_prepared), row_sums, reinterpret_cast<uint32_t*>(ws),
+                 (int)(kW4CounterBytes / 4), (int)K))
+    return -1;
   const bool sgn = signed_nibbles != 0;
   switch (mt) {
     case 16: return launch_w4i8<16>(sgn, tmW, tmA, p, (int)grid, s);
@@ -831,20 +831,12 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     // Launched as a programmatic dependent too: behind another call of this operator (whose GEMM kernel lets its
     // dependents go at once) the pre-pass is already resident, waiting, when that call ends, and the GEMM kernel
     // behind it sets up and streams its first weights meanwhile.  Behind any other kernel this is plain stream order.
-    static const int chain = getenv("QGEMM_PDL_CHAIN") ? atoi(getenv("QGEMM_PDL_CHAIN")) : 1;
     const uint4* a_in = static_cast<const uint4*>(A);
     uint4* a_out = reinterpret_cast<uint4*>(a_prepared);
     const int is_bf = a_dtype == QGEMM_DT_BF16 ? 1 : 0, permute = weight_format == QGEMM_W4_SEQUENTIAL ? 1 : 0;
-    const int n_counters = (int)(kW4CounterBytes / 4);
-    if (chain) {
-      if (launch_pdl(qg::w4a16_prepare_activations, (int)blocks, 256, 0, s, a_in, a_out, n_chunks, is_bf, permute,
-                     p.ws_counters, n_counters))
-        return -1;
-    } else {
-      qg::w4a16_prepare_activations<<<(unsigned)blocks, 256, 0, s>>>(a_in, a_out, n_chunks, is_bf, permute,
-                                                                    p.ws_counters, n_counters);
-      CUDA_OK(cudaGetLastError());
-    }
+    if (launch_pdl(qg::w4a16_prepare_activations, (int)blocks, 256, 0, s, a_in, a_out, n_chunks, is_bf, permute,
+                   p.ws_counters, (int)(kW4CounterBytes / 4)))
+      return -1;
   }
   if (dequant_once) {
     uint8_t* w16 = a_prepared + batch * M * K * 2;

@@ -257,6 +257,7 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
                   const __grid_constant__ CUtensorMap tmA, const W4A16Params p) {
   using Cfg = W4Cfg<MT>;
+  pdl_launch_dependents();  // the next call's pre-pass may become resident; it waits for this grid before it writes
   constexpr int RS = Cfg::RAW_STAGES;
   constexpr int AS = Cfg::A_STAGES;
   constexpr int WS = Cfg::W_STAGES;

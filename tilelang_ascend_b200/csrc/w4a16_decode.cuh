@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(W4D_THREADS, 1)
 w4a16_decode_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
                     const __grid_constant__ CUtensorMap tmA, const W4A16Params p) {
   using Cfg = W4DCfg<NB>;
+  pdl_launch_dependents();  // the next call's pre-pass may become resident; it waits for this grid before it writes
   constexpr int MT = Cfg::MT;
   constexpr int ST = Cfg::STAGES;
   constexpr bool SCALED = FLUSH != 0;

@@ -54,6 +54,7 @@ w4a8_prepare_activations(const uint2* __restrict__ in, uint2* __restrict__ out, 
                          uint32_t* __restrict__ counters, int n_counters, int K) {
   __shared__ int red[8];
   pdl_launch_dependents();
+  pdl_wait();  // behind another call of this operator: that call's kernel still reads the scratch until it is done
   // the caller's scratch holds anything: the arrival counters start at zero
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_counters; i += gridDim.x * blockDim.x) counters[i] = 0u;
   const int m = blockIdx.x;
@@ -82,6 +83,7 @@ __global__ void __launch_bounds__(W4_THREADS, 1)
 w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
                  const W4A8Params p) {
   using Cfg = W4I8Cfg<MT>;
+  pdl_launch_dependents();  // the next call's pre-pass may become resident; it waits for this grid before it writes
   constexpr int RS = Cfg::RAW_STAGES;
   constexpr int AS = Cfg::A_STAGES;
   constexpr int WS = Cfg::W_STAGES;
