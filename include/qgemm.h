@@ -111,7 +111,7 @@ int qgemm_w8a8_grouped(const int8_t* A, const int8_t* B, const float* scale_b, c
                        int b_layout, uint32_t* status, void* stream);
 
 /* Bytes of scratch memory qgemm_w4a16 needs for this problem on the current device (split-K partial
- * sums and arrival counters, the prepared activations and, from 1024 tokens on, the weights as f16: 2*N*K).
+ * sums and arrival counters, the prepared activations and, from 1792 tokens on, the weights as f16: 2*N*K).
  * The buffer needs no initialisation: every call zeroes the qgemm_w4a16_counter_bytes() bytes of arrival
  * counters at its start, on the stream, and writes everything else before reading it.  Two launches
  * that may overlap on the device must not share a scratch buffer. */
@@ -174,9 +174,13 @@ int qgemm_w4a16_batched(const void* A, const uint8_t* B_packed, const void* scal
  *                QGEMM_ZERO_RESCALE    W = q * s - |z|      (one f16 FMA; needs the zeros tensor)
  *                QGEMM_ZERO_QUANTIZED  W = (q - qz) * s     with integer qz given as fp16 values (unpack
  *                                      packed qzeros on the host first)
- * With a zeros tensor the weights are dequantised once into the scratch buffer (f16 [batch, N, K]) and
- * multiplied by the f16 tensor-core GEMM at every token count, so the scratch size comes from
- * qgemm_w4a16_ex_workspace_bytes(..., has_zeros_tensor = 1).  Without one, the same kernels as qgemm_w4a16 run.
+ * A zeros tensor of mode QGEMM_ZERO_QUANTIZED (integer zero points 0..15) is taken in flight by the streaming kernel
+ * when M <= 64 and the groups are 128 wide, a multiple of 256 or the whole K: no dequantised copy of the weights,
+ * (q - qz) exact, and a scratch buffer of qgemm_w4a16_ex_workspace_bytes(..., has_zeros_tensor = 0) suffices.
+ * Otherwise a zeros tensor makes the operator dequantise the weights once into the scratch buffer
+ * (f16 [batch, N, K]) and multiply with the f16 tensor-core GEMM, whatever the token count; that scratch size comes
+ * from qgemm_w4a16_ex_workspace_bytes(..., has_zeros_tensor = 1).  Without a zeros tensor the same kernels as
+ * qgemm_w4a16 run.
  */
 #define QGEMM_W4_SEQUENTIAL 0
 #define QGEMM_W4_INTERLEAVED_F16 1

@@ -64,6 +64,11 @@ W4_SHAPES = [
     (100, 512, 136, 256),
     (256, 1024, 256, 128),
     (300, 768, 520, -1),
+    # two blocks of 128 tokens per tile (above 128 tokens): ragged second block, odd and even block counts, split K
+    (130, 512, 272, 128),
+    (200, 2048, 136, 32),
+    (513, 1024, 264, 64),
+    (640, 4096, 384, 128),
 ]
 
 
@@ -235,7 +240,7 @@ def test_rejects_bad_arguments():
 
 
 def test_dequantise_once_path_small_shapes():
-    """Above QGEMM_W4_GEMM_MIN_M tokens (default 1024) the weights are dequantised to f16 once and multiplied by
+    """Above QGEMM_W4_GEMM_MIN_M tokens (default 1792) the weights are dequantised to f16 once and multiplied by
     the f16 tensor-core GEMM.  The threshold is read once per process, so a child process with a low threshold
     runs that path on small ragged shapes: scaled / unscaled, every group size, f16 / bf16, batched."""
     import os

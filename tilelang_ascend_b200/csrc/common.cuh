@@ -124,6 +124,15 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, c
   return ok != 0;
 }
 
+// One lane of a converged warp, chosen by the hardware (the same lane every time for the same mask).  Code under
+// `if (elect_one_sync())` is known to the compiler to run in exactly one lane, which lets it issue tcgen05.mma /
+// commit / TMA instructions with their operands in uniform registers.
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 // ------------------------------------------------- programmatic dependent launch
 // A kernel launched with the programmatic-stream-serialization attribute may start once every block of the
 // kernel in front of it has executed pdl_launch_dependents() (or exited); whatever it reads from that kernel

@@ -90,10 +90,6 @@ int set_smem_w4() {
   using C = qg::W4Cfg<MT>;
   if (set_smem(qg::w4a16_gemm_kernel<MT, false>, C::SMEM_BYTES)) return -1;
   if (set_smem(qg::w4a16_gemm_kernel<MT, true>, C::SMEM_BYTES)) return -1;
-  if constexpr (MT == 128) {
-    if (set_smem(qg::w4a16_gemm_kernel<MT, false, true>, C::SMEM_BYTES)) return -1;
-    if (set_smem(qg::w4a16_gemm_kernel<MT, true, true>, C::SMEM_BYTES)) return -1;
-  }
   return 0;
 }
 
@@ -217,19 +213,6 @@ int launch_w4(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUt
   if (bf) return launch_pdl(qg::w4a16_gemm_kernel<MT, true>, grid, qg::W4_THREADS, qg::W4Cfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p);
   return launch_pdl(qg::w4a16_gemm_kernel<MT, false>, grid, qg::W4_THREADS, qg::W4Cfg<MT>::SMEM_BYTES, s, tmW, tmS, tmA, p);
 }
-// 128-token tile with two blocks of weight rows per tile (see the kernel's PAIR parameter)
-int launch_w4_pair(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
-                   const qg::W4A16Params& p, int grid, cudaStream_t s) {
-  if (bf) return launch_pdl(qg::w4a16_gemm_kernel<128, true, true>, grid, qg::W4_THREADS, qg::W4Cfg<128>::SMEM_BYTES, s, tmW, tmS, tmA, p);
-  return launch_pdl(qg::w4a16_gemm_kernel<128, false, true>, grid, qg::W4_THREADS, qg::W4Cfg<128>::SMEM_BYTES, s, tmW, tmS, tmA, p);
-}
-// Above 64 tokens (128-token tiles) a tile takes two blocks of 128 weight rows when the matrix has at least two.
-// QGEMM_W4_PAIR=0 keeps one block per tile.
-bool w4_use_pair(int mt, int64_t N) {
-  static const int on = getenv("QGEMM_W4_PAIR") ? atoi(getenv("QGEMM_W4_PAIR")) : 1;
-  return on && mt == 128 && N > 128;
-}
-
 // Test hook (qgemm_debug_withhold_commit): see W4GDebug.
 int g_w4g_withhold_commit = 0;
 
@@ -569,13 +552,14 @@ int qgemm_w8a8_grouped(const int8_t* A, const int8_t* B, const float* scale_b, c
 int64_t qgemm_w4a16_counter_bytes(void) { return kW4CounterBytes; }
 
 // Token counts from this on (and N a multiple of 16) dequantise the whole weight matrix to f16 once and run
-// the f16 tensor-core GEMM on it: above a few hundred tokens the in-flight conversion, repeated for every
-// 128-token tile, costs more than writing and re-reading 2 bytes per weight.  QGEMM_W4_GEMM_MIN_M overrides
-// the threshold (0 = never).
+// the f16 tensor-core GEMM on it: the in-flight conversion is repeated for every 128-token tile and at some point
+// costs more than writing and re-reading 2 bytes per weight.  Measured sweep on K=8192, N=28672 (in-flight against
+// dequantise-once, us): 512 tokens 230 / 366, 1024: 445 / 526, 1536: 685 / 710, 2048: 927 / 877 - the paths cross
+// near 1800.  QGEMM_W4_GEMM_MIN_M overrides the threshold (0 = never).
 int64_t w4_gemm_min_m() {
   static int64_t v = -1;
   if (v < 0) {
-    v = 1024;
+    v = 1792;
     if (const char* e = getenv("QGEMM_W4_GEMM_MIN_M")) v = atoll(e) > 0 ? atoll(e) : (1ll << 62);
     if (v <= 16) v = 17;  // the small-token kernels keep their range
   }
@@ -589,11 +573,10 @@ static int64_t w4_workspace_bytes(int64_t batch, int64_t M, int64_t N, int64_t K
   const int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
   // sized for whichever small-token kernel the scale groups will select (the group-sum kernel's tile is the taller)
   const int mt = M <= 64 ? w4_pick_mt(M, true) : w4_pick_mt(M, false);
-  const int slot_rows = w4_use_pair(mt, N) ? 2 * mt : mt;  // two blocks of weight rows per tile: twice the partial sums
   // the arrival counters first (fixed place whatever the tile height), then two partial slots of
   // [MT][128] fp32 per CTA, then the f16 copy of the activations in the kernel's K order
   // ... and, for the large-token path, the dequantised f16 weights
-  return kW4CounterBytes + grid * 2 * (int64_t)slot_rows * 128 * 4 + batch * M * K * 2 +
+  return kW4CounterBytes + grid * 2 * (int64_t)mt * 128 * 4 + batch * M * K * 2 +
          ((dequant_once || w4_use_f16_gemm(M, N)) ? batch * N * K * 2 : 0);
 }
 
@@ -755,7 +738,8 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
   const bool zeros_inflight = zeros != nullptr && zeros_inflight_on && zero_mode == QGEMM_ZERO_QUANTIZED && gd == nullptr &&
                               !w4_use_f16_gemm(M, N) && w4_gs_shape_ok(M, true, group, K);
   const bool dequant_once = (zeros != nullptr && !zeros_inflight) || w4_use_f16_gemm(M, N);
-  const int64_t need = w4_workspace_bytes(batch, M, N, K, zeros != nullptr);
+  // a zeros tensor that is taken in flight needs no room for dequantised weights
+  const int64_t need = w4_workspace_bytes(batch, M, N, K, zeros != nullptr && !zeros_inflight);
   if (need < 0) return -1;
   if (workspace == nullptr || workspace_bytes < need) return fail("qgemm_w4a16: workspace of %lld bytes needed (got %lld)", (long long)need, (long long)workspace_bytes);
 
@@ -787,8 +771,7 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
       return -1;
   }
   const int64_t grid_max = sms < kW4MaxGrid ? sms : kW4MaxGrid;
-  const bool pair = !dequant_once && !use_gs && w4_use_pair(mt, N);
-  uint8_t* a_prepared = static_cast<uint8_t*>(workspace) + kW4CounterBytes + grid_max * 2 * (int64_t)(pair ? 2 * mt : mt) * 128 * 4;
+  uint8_t* a_prepared = static_cast<uint8_t*>(workspace) + kW4CounterBytes + grid_max * 2 * (int64_t)mt * 128 * 4;
   {
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)batch};
     const uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)M * (uint64_t)K * 2};
@@ -816,7 +799,7 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
   p.zero = zero;
   p.has_scales = scales != nullptr;
   p.m_tiles = (int)((M + mt - 1) / mt);
-  p.n_tiles = pair ? (int)((N + 255) / 256) : (int)((N + 127) / 128);
+  p.n_tiles = (int)((N + 127) / 128);
   p.batch = (int)batch;
   const int64_t num_tiles = batch * (int64_t)p.m_tiles * p.n_tiles;
   if (num_tiles > 0x3fffffff) return fail("qgemm_w4a16: too many tiles");
@@ -886,9 +869,7 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
     case 16: return launch_w4<16>(bf, tmW, tmS, tmA, p, (int)grid, s);
     case 32: return launch_w4<32>(bf, tmW, tmS, tmA, p, (int)grid, s);
     case 64: return launch_w4<64>(bf, tmW, tmS, tmA, p, (int)grid, s);
-    default:
-      if (pair) return launch_w4_pair(bf, tmW, tmS, tmA, p, (int)grid, s);
-      return launch_w4<128>(bf, tmW, tmS, tmA, p, (int)grid, s);
+    default: return launch_w4<128>(bf, tmW, tmS, tmA, p, (int)grid, s);
   }
 }
 

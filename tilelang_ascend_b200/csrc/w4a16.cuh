@@ -74,10 +74,16 @@ struct W4Cfg {
   // so MMAW warps issue the K steps of a slab in parallel, each into its own accumulator; the epilogue adds
   // the MMAW accumulators in a fixed order.
   static constexpr int MMAW = (MT <= 32) ? 4 : (MT == 64 ? 2 : 1);
+  // Two accumulator sets: the epilogue of a segment overlaps the next segment's MMAs.  (One set was measured for
+  // the 128-token tile in three forms that need the room - two issuers, two blocks of tokens per converted slab,
+  // two blocks of weight rows per activation stage: 290 us each at 512 tokens, N=28672, against 228 us; a tile is
+  // only 32 slabs long, and draining and refilling the pipeline at every segment end costs more than any of them
+  // saves.)
+  static constexpr int ACC_BUFS = 2;
   static constexpr int W_STAGES = (MT == 16) ? 3 : 2;
   static constexpr int A_KB_BYTES = MT * 128;          // one 64-wide K block of activations
   static constexpr int A_BYTES = 4 * A_KB_BYTES;       // one 256-wide slab
-  static constexpr int ACC_COLS = 2 * MMAW * MT;       // two buffers of MMAW accumulators
+  static constexpr int ACC_COLS = ACC_BUFS * MMAW * MT;  // ACC_BUFS sets of MMAW accumulators
   static constexpr int TMEM_COLS = 512;
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_BYTES = RAW_STAGES * W4_RAW_BYTES + A_STAGES * A_BYTES + BAR_BYTES + 1024;
@@ -252,20 +258,11 @@ w4a16_prepare_activations(const uint4* __restrict__ in, uint4* __restrict__ out,
 
 __device__ __forceinline__ void w4_epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-// PAIR = true (128-token tile only): a tile is TWO blocks of 128 weight rows that share every activation stage.
-// With one block per tile the kernel waits for its activations (a 64 KB stage per slab, two stages, the refill of
-// a stage starting only when the slab's MMAs have completed: measured 2660 cycles per slab against 1024 of MMAs and
-// 1400 of conversion); two blocks per stage halve the activation bytes per MMA and double the MMA time a refill may
-// take.  Both blocks' accumulators (2 x 128 columns) then fill the accumulator space, so they are not double
-// buffered: the MMAs of a CTA's next segment wait for the epilogue of this one.  The raw ring, the dequant warps and
-// the weight stages simply see twice as many slabs (block 0, block 1 of every K slab in turn).
-template <int MT, bool OUT_BF16, bool PAIR = false>
+template <int MT, bool OUT_BF16>
 __global__ void __launch_bounds__(W4_THREADS, 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
                   const __grid_constant__ CUtensorMap tmA, const W4A16Params p) {
   using Cfg = W4Cfg<MT>;
-  static_assert(!PAIR || (MT == 128 && Cfg::MMAW == 1), "row pairs: 128-token tile, one issuer");
-  constexpr int NRB = PAIR ? 2 : 1;  // blocks of 128 weight rows per tile
   pdl_launch_dependents();  // the next call's pre-pass may become resident; it waits for this grid before it writes
   constexpr int RS = Cfg::RAW_STAGES;
   constexpr int AS = Cfg::A_STAGES;
@@ -345,21 +342,18 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       while (ok && seg.next(tile, ks0, ks1)) {
         int b, n0, m0;
         w4_tile_coords(p, tile, MT, b, n0, m0);
-        n0 *= NRB;
-        for (int ks = ks0; ok && ks < ks1; ++ks) {
-          for (int rb = 0; rb < NRB; ++rb) {
-            if (!mbar_wait(&raw_empty[rs], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
-            uint8_t* dst = raw_base + rs * W4_RAW_BYTES;
-            mbar_arrive_expect_tx(&raw_full[rs], tx);
-            tma_load_3d(dst, &tmW, &raw_full[rs], ks * (W4_SLAB_K / 2), n0 + rb * W4_BN, b);
-            if (p.has_scales) {
-              const int srow = (p.group <= W4_SLAB_K) ? ks * p.scale_rows : (ks * W4_SLAB_K) / p.group;
-              tma_load_3d(dst + W4_RAW_PACKED, &tmS, &raw_full[rs], n0 + rb * W4_BN, srow, b);
-            }
-            issued_mask |= 1u << rs;
-            parity_mask = (parity_mask & ~(1u << rs)) | (phase << rs);
-            if (++rs == RS) { rs = 0; phase ^= 1u; }
+        for (int ks = ks0; ks < ks1; ++ks) {
+          if (!mbar_wait(&raw_empty[rs], phase ^ 1u, ctl, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* dst = raw_base + rs * W4_RAW_BYTES;
+          mbar_arrive_expect_tx(&raw_full[rs], tx);
+          tma_load_3d(dst, &tmW, &raw_full[rs], ks * (W4_SLAB_K / 2), n0, b);
+          if (p.has_scales) {
+            const int srow = (p.group <= W4_SLAB_K) ? ks * p.scale_rows : (ks * W4_SLAB_K) / p.group;
+            tma_load_3d(dst + W4_RAW_PACKED, &tmS, &raw_full[rs], n0, srow, b);
           }
+          issued_mask |= 1u << rs;
+          parity_mask = (parity_mask & ~(1u << rs)) | (phase << rs);
+          if (++rs == RS) { rs = 0; phase ^= 1u; }
         }
       }
       if (!ok) {
@@ -422,7 +416,13 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     //    kk = w, w + MMAW, ... of every slab.  Following every slab just to keep the parity waits safe made
     //    round robin no faster there (measured), and those tiles are bound by the dequant warps anyway.
     const int mw = (warp == 1) ? 0 : (warp - W4_FIRST_XMMA_WARP + 1);
-    if (mw < Cfg::MMAW && lane == 0) {
+    // The issuing warps run converged: all lanes wait, one hardware-elected lane (always the same one) issues.  Under
+    // `if (elect_one_sync())` the compiler knows a single lane runs and keeps descriptors in uniform registers.  Issue
+    // time is what matters here: one thread needs 100-130 cycles per tcgen05.mma with the dequant warps competing for
+    // issue slots, i.e. ~2000 cycles for a slab's 16 MMAs, which themselves run for 1024 (ablations at 512 tokens,
+    // N=28672: 284 us; 173 us without the MMAs; 232 us without the conversion arithmetic).  The elected lane took
+    // that case from 284 to 228 us.
+    if (mw < Cfg::MMAW) {
       constexpr uint32_t idesc = make_idesc(ACC_F32, FMT_F16, FMT_F16, 0, 0, W4_BN, MT);
       const uint64_t desc_hi = make_desc_kmajor(0);  // K-major activation descriptor without its start address
       const uint32_t a_base_u32 = smem_u32(a_base);
@@ -435,54 +435,47 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       int turn = 0;  // slab index % MMAW
       bool ok = true;
       while (ok && seg.next(tile, ks0, ks1)) {
-        // row pairs: one set of accumulators (block rb at columns rb * MT), a phase per segment
-        const int buf = PAIR ? 0 : (it & 1);
-        const uint32_t tphase = PAIR ? (uint32_t)(it & 1) : (uint32_t)((it >> 1) & 1);
-        if (!mbar_wait(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+        const int buf = it % Cfg::ACC_BUFS;
+        const uint32_t tphase = (uint32_t)(it / Cfg::ACC_BUFS) & 1u;
+        if (!mbar_wait_warp(&tempty[buf], tphase ^ 1u, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d = tmem_base + buf * (Cfg::MMAW * MT) + mw * MT;
         uint32_t started = 0;  // 0 for this issuer's first MMA of the segment: overwrite the accumulator
-        for (int ks = ks0; ok && ks < ks1; ++ks) {
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!ROUND_ROBIN || turn == mw) {
-            if (!mbar_wait(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+            if (!mbar_wait_warp(&a_full[as], aphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+            if (!mbar_wait_warp(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
+            tc_fence_after_sync();
             const uint64_t adesc0 = desc_hi | (uint64_t)(((a_base_u32 + as * Cfg::A_BYTES) & 0x3FFFFu) >> 4);
-            const uint32_t started_ks = started;
-#pragma unroll
-            for (int rb = 0; rb < NRB; ++rb) {
-              if (!mbar_wait(&w_full[ws], wphase, ctl, ST_TIMEOUT_MMA)) { ok = false; break; }
-              tc_fence_after_sync();
-              const uint32_t tW = tmem_w + ws * W4_W_COLS;
-              constexpr int STEPS = ROUND_ROBIN ? W4_SLAB_K / 16 : (W4_SLAB_K / 16) / Cfg::MMAW;
-              started = started_ks;
+            const uint32_t tW = tmem_w + ws * W4_W_COLS;
+            constexpr int STEPS = ROUND_ROBIN ? W4_SLAB_K / 16 : (W4_SLAB_K / 16) / Cfg::MMAW;
+            if (elect_one_sync()) {
 #pragma unroll
               for (int j = 0; j < STEPS; ++j) {  // 16 k per MMA: 8 TMEM columns, 32 bytes of smem
                 const int kk = ROUND_ROBIN ? j : j * Cfg::MMAW + mw;
                 const uint32_t off = (uint32_t)(((kk >> 2) * Cfg::A_KB_BYTES + (kk & 3) * 32) >> 4);
-                umma_f16_ts(d + rb * MT, tW + kk * 8, adesc0 + off, idesc, started);
-                started = 1u;
+                umma_f16_ts(d, tW + kk * 8, adesc0 + off, idesc, j == 0 ? started : 1u);
               }
               umma_commit(&w_empty[ws]);
-              if (PAIR) {  // the next block's weights are the next weight stage
-                if (++ws == WS) { ws = 0; wphase ^= 1u; }
-              }
+              umma_commit(&a_empty[as]);
             }
-            if (!ok) break;
-            umma_commit(&a_empty[as]);
+            started = 1u;
           }
           if (++turn == Cfg::MMAW) turn = 0;
-          if (!PAIR) {
-            if (++ws == WS) { ws = 0; wphase ^= 1u; }
-          }
+          if (++ws == WS) { ws = 0; wphase ^= 1u; }
           if (++as == AS) { as = 0; aphase ^= 1u; }
         }
-        if (ok) umma_commit(&tfull[buf]);
+        // the elected lane is the same one every time, so this commit covers the MMAs issued above
+        if (ok && elect_one_sync()) umma_commit(&tfull[buf]);
         ++it;
       }
       if (!ok && mw == 0) {
-        umma_commit(drain);
-        const uint64_t t0 = global_timer_ns();
-        while (!mbar_try_wait(drain, 0)) {
-          if (global_timer_ns() - t0 > p.wait_limit_ns) break;
+        if (elect_one_sync()) umma_commit(drain);
+        if (lane == 0) {
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait(drain, 0)) {
+            if (global_timer_ns() - t0 > p.wait_limit_ns) break;
+          }
         }
       }
     }
@@ -496,26 +489,24 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     constexpr bool ROUND_ROBIN_E = (WS % Cfg::MMAW) == 0 && (AS % Cfg::MMAW) == 0;  // as in the MMA issuers
     long long first_slab = 0;  // CTA-local index of the segment's first slab: issuer (first_slab + i) % MMAW took slab i
     while (seg.next(tile, ks0, ks1)) {
-      const int buf = PAIR ? 0 : (it & 1);
-      const uint32_t tphase = PAIR ? (uint32_t)(it & 1) : (uint32_t)((it >> 1) & 1);
+      const int buf = it % Cfg::ACC_BUFS;
+      const uint32_t tphase = (uint32_t)(it / Cfg::ACC_BUFS) & 1u;
       ++it;
       const int seg_len = ks1 - ks0;
       const int first_turn = (int)(first_slab % Cfg::MMAW);
       first_slab += seg_len;
       int b, n0, m0;
       w4_tile_coords(p, tile, MT, b, n0, m0);
-      n0 *= NRB;
+      const int n = n0 + nl;
       uint16_t* Cout = reinterpret_cast<uint16_t*>(p.C) + (size_t)b * p.M * p.N;
       const bool full_tile = (ks0 == 0 && ks1 == p.KS);
       const int my_slot = (ks1 < p.KS) ? 2 * cta + 1 : 2 * cta;
       const bool ok = mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE);
       if (ok) {
         tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (Cfg::MMAW * MT);
 #pragma unroll 1
-        for (int cc = 0; cc < NRB * (MT / CH); ++cc) {
-          const int rb = cc / (MT / CH), c = cc % (MT / CH);  // block of weight rows, chunk of token columns
-          const int n = n0 + rb * W4_BN + nl;
-          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (Cfg::MMAW * MT) + rb * MT;
+        for (int c = 0; c < MT / CH; ++c) {
           uint32_t r[CH];
 #pragma unroll
           for (int j = 0; j < CH; ++j) r[j] = 0u;  // +0.0f
@@ -543,7 +534,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
               }
             }
           } else {
-            float* dst = p.ws_partials + (size_t)my_slot * (NRB * MT * W4_BN) + (size_t)(rb * MT + c * CH) * W4_BN + nl;
+            float* dst = p.ws_partials + (size_t)my_slot * (MT * W4_BN) + (size_t)(c * CH) * W4_BN + nl;
 #pragma unroll
             for (int j = 0; j < CH; ++j) dst[j * W4_BN] = __uint_as_float(r[j]);
           }
@@ -582,10 +573,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const bool is_last = (ctrl & 2u) != 0;
       if (is_last) {
         __threadfence();
-#pragma unroll 1
-        for (int rb = 0; rb < NRB; ++rb) {
-          const int n = n0 + rb * W4_BN + nl;
-          if (n >= p.N) continue;
+        if (n < p.N) {
           // Fixed summation order (contributor b_first .. b_last); per contributor all MT loads are issued
           // before the first add so that their latencies overlap.
           constexpr int RU = 16;
@@ -599,7 +587,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
             for (int c = b_first; c <= b_last; ++c) {
               const long long c_end = w4_range_begin(T, G, c + 1);
               const int slot = (c_end >= first_item + p.KS) ? 2 * c : 2 * c + 1;
-              const float* src = p.ws_partials + (size_t)slot * (NRB * MT * W4_BN) + (size_t)(rb * MT + mb) * W4_BN + nl;
+              const float* src = p.ws_partials + (size_t)slot * (MT * W4_BN) + (size_t)mb * W4_BN + nl;
               float v[RU];
 #pragma unroll
               for (int u = 0; u < RU; ++u) v[u] = (mb + u < rows) ? __ldcg(src + u * W4_BN) : 0.0f;
@@ -637,7 +625,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     uint32_t rphase = 0, wphase = 0;
     bool ok = true;
     while (ok && seg.next(tile, ks0, ks1)) {
-      for (int kv = NRB * ks0; kv < NRB * ks1; ++kv) {  // every block of every K slab, in the raw producer's order
+      for (int ks = ks0; ks < ks1; ++ks) {
         if (!mbar_wait_warp(&raw_full[rs], rphase, ctl, ST_TIMEOUT_DEQUANT)) { ok = false; break; }
         const uint8_t* rawp = raw_base + rs * W4_RAW_BYTES;
         const uint4 v0 = *reinterpret_cast<const uint4*>(rawp + off0);

@@ -18,6 +18,7 @@ Every call goes through the C ABI of libqgemm.so; there is no fallback path.
 from __future__ import annotations
 
 import functools
+import os
 from typing import Optional
 
 import torch
@@ -287,7 +288,12 @@ def w4a16_gemm(A, B_packed, scales=None, zeros=8, group_size=128, out_dtype=None
     if check_status and status is None:
         status = torch.zeros(1, dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
-        ws, need = _w4a16_workspace(lib, batch, M, N, K, dev, sh, zeros_t is not None)
+        # integer zero points at decode sizes are taken in flight: no room for dequantised weights is needed
+        inflight = (zeros_t is not None and zeros_mode == "quantized" and M <= 64
+                    and (group_size == 128 or group_size % 256 == 0 or group_size >= K)
+                    and os.environ.get("QGEMM_W4_ZEROS_INFLIGHT", "1") != "0" and os.environ.get("QGEMM_W4_GS", "1") != "0"
+                    and "QGEMM_W4_GS_MIN_M" not in os.environ)
+        ws, need = _w4a16_workspace(lib, batch, M, N, K, dev, sh, zeros_t is not None and not inflight)
         rc = lib.qgemm_w4a16_ex(A.data_ptr(), B_packed.data_ptr(), _ptr(scales), _ptr(zeros_t), int(zeros),
                                 _ZERO_MODES[zeros_mode], _WEIGHT_LAYOUTS[weight_layout], int(group_size),
                                 C.data_ptr(), ws.data_ptr(), need, batch, M, N, K, _ABI_DT[A.dtype],
