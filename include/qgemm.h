@@ -277,6 +277,21 @@ int qgemm_w4a8(const int8_t* A, const uint8_t* qB, int8_t* workspace, void* C, i
                int signed_nibbles, int out_dtype, uint32_t* status, void* stream);
 
 /*
+ * W4A8 with the per-token activation quantiser fused into its pre-pass (decode sizes, M <= 128):
+ *   scale_a[m] = max(max_k |X[m,k]|, 1e-4) / 127   (round_scale: rounded up to a power of two)
+ *   A[m,k]     = int8(rint(X[m,k] / scale_a[m]))   (never written to memory in the caller's layout)
+ *   C[m,n]     = sum_k int32(A[m,k]) * int32(unpack(qB)[n,k])
+ * i.e. qgemm_act_quant followed by qgemm_w4a8 in one call, with bit-identical scale_a and C: the reference's
+ * act_quant_kernel_int8_optimized (examples/deepseek_v4/act_quant.py:33-92) in front of w4a8_gemm_cv
+ * (examples/dequantize_gemm/example_dequant_gemm_w4a8.py:25-121), saving one launch and the int8 round trip.
+ * X is [M, K] f16 or bf16, scale_a [M] fp32 (output), workspace the [N, K] int8 scratch of qgemm_w4a8.
+ * No reference counterpart as a single operator.
+ */
+int qgemm_w4a8_act_quant(const void* X, int x_dtype, const uint8_t* qB, int8_t* workspace, int32_t* C, float* scale_a,
+                         int round_scale, int64_t M, int64_t N, int64_t K, int signed_nibbles, uint32_t* status,
+                         void* stream);
+
+/*
  * Per-token activation quantiser, the step in front of the W8A8 GEMM: it produces that GEMM's A and scale_a.
  * Replaces the compiled `call` of act_quant_kernel_int8_optimized (examples/deepseek_v4/act_quant.py:33-92)
  * and follows its golden act_quant_torch (:112-142) bit for bit:

@@ -84,3 +84,43 @@ def test_factory_signature_and_errors():
         q.act_quant(torch.zeros(4, 64, dtype=torch.float32, device="cuda"))
     with pytest.raises(q.QGemmError):
         q.act_quant(torch.zeros(4, 12, dtype=torch.bfloat16, device="cuda"))
+
+
+@pytest.mark.parametrize("M,K,N,dtype,round_scale", [(1, 1024, 4096, torch.bfloat16, False), (16, 8192, 1024, torch.bfloat16, False),
+                                                     (37, 4096, 2560, torch.float16, True), (128, 2048, 10240, torch.bfloat16, False),
+                                                     (5, 16384 + 256, 272, torch.float16, False)])
+def test_quantiser_fused_into_the_w4a8_operator(M, K, N, dtype, round_scale):
+    """bf16 / f16 activations straight into the W4A8 operator: scales and int32 results are those of the oracle's
+    act_quant followed by its W4A8 GEMM, bit for bit, and of the two separate device calls."""
+    g = torch.Generator().manual_seed(M + K + N)
+    x = (torch.randn(M, K, generator=g) * torch.rand(M, 1, generator=g) * 4).to(dtype)
+    qB = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)
+    a8_ref, sa_ref = oc.act_quant_torch_ref(x, round_scale=round_scale)
+    C_ref = oc.w4a8_gemm_ref(a8_ref, qB)
+    ws = torch.empty((N, K), dtype=torch.int8, device="cuda")
+    C = torch.empty((M, N), dtype=torch.int32, device="cuda")
+    kernel = q.w4a8_gemm_act_quant(M, N, K, round_scale=round_scale)
+    C, sa = kernel(x.cuda(), qB.cuda(), ws, C)
+    assert torch.equal(sa.cpu(), sa_ref.view(-1))
+    assert torch.equal(C.cpu(), C_ref)
+    a8, sa2 = q.act_quant(x.cuda(), round_scale=round_scale)
+    C2 = q.w4a8_gemm_cv(M, N, K)(a8, qB.cuda(), ws, torch.empty_like(C))
+    assert torch.equal(C, C2) and torch.equal(sa, sa2.view(-1))
+
+
+def test_fused_quantiser_needs_room_for_its_scratch_in_the_workspace():
+    """The [N, K] int8 workspace is the only scratch the operator gets; a weight matrix smaller than the kernel's own
+    scratch (a few MB) is rejected with a message instead of being overrun."""
+    M, K, N = 4, 256, 128
+    kernel = q.w4a8_gemm_act_quant(M, N, K)
+    with pytest.raises(q.QGemmError, match="workspace is too small"):
+        kernel(torch.zeros((M, K), dtype=torch.bfloat16, device="cuda"), torch.zeros((N, K // 2), dtype=torch.uint8, device="cuda"),
+               torch.empty((N, K), dtype=torch.int8, device="cuda"), torch.empty((M, N), dtype=torch.int32, device="cuda"))
+
+
+def test_fused_quantiser_rejects_more_than_128_tokens():
+    M, K, N = 129, 256, 128
+    kernel = q.w4a8_gemm_act_quant(M, N, K)
+    with pytest.raises(q.QGemmError, match="M <= 128"):
+        kernel(torch.zeros((M, K), dtype=torch.bfloat16, device="cuda"), torch.zeros((N, K // 2), dtype=torch.uint8, device="cuda"),
+               torch.empty((N, K), dtype=torch.int8, device="cuda"), torch.empty((M, N), dtype=torch.int32, device="cuda"))

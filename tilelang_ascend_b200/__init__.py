@@ -19,6 +19,7 @@ from .ops import (  # noqa: F401
     unpack_int4,
     w4a16_gemm,
     w4a8_gemm_cv,
+    w4a8_gemm_act_quant,
 )
 from .quantize import (  # noqa: F401
     deinterleave_weight_int4_f16,

@@ -60,6 +60,8 @@ SIGNATURES = {
     "qgemm_unpack_int4": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int, _c.c_void_p]),
     "qgemm_w4a8": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64,
                               _c.c_int64, _c.c_int, _c.c_int, _c.c_void_p, _c.c_void_p]),
+    "qgemm_w4a8_act_quant": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int,
+                                        _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_void_p, _c.c_void_p]),
     "qgemm_act_quant": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
                                    _c.c_void_p]),
 }

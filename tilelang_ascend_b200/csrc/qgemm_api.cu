@@ -333,8 +333,11 @@ static int launch_w4i8(bool sgn, const CUtensorMap& tmW, const CUtensorMap& tmA,
 // Fused path of qgemm_w4a8 for up to 128 tokens: no int8 copy of the weights; the caller's [N, K] workspace
 // only holds the small scratch (arrival counters, int32 partial sums, reordered activations, row sums).
 // Returns 1 when the problem does not qualify (the caller then takes the two-kernel path).
+// `A` int8 [M, K]; or, with `X` non-null, bf16 / f16 activations that the pre-pass quantises per token itself
+// (scales to `scale_out`).
 static int w4a8_fused(const int8_t* A, const uint8_t* qB, int8_t* workspace, int* C, int64_t M, int64_t N, int64_t K,
-                      int signed_nibbles, uint32_t* status, cudaStream_t s) {
+                      int signed_nibbles, uint32_t* status, cudaStream_t s, const void* X = nullptr, int x_is_bf16 = 0,
+                      int round_scale = 0, float* scale_out = nullptr) {
   static const int enabled = getenv("QGEMM_W4A8_FUSED") ? atoi(getenv("QGEMM_W4A8_FUSED")) : 1;
   if (!enabled || M > 128 || !aligned16(workspace)) return 1;
   int sms = 0;
@@ -377,9 +380,14 @@ static int w4a8_fused(const int8_t* A, const uint8_t* qB, int8_t* workspace, int
   p.wait_limit_ns = g_wait_limit_ns;
   int64_t grid = grid_max < p.total_items ? grid_max : p.total_items;
   // a programmatic dependent of whatever is in front: behind another call of this operator it is resident early
-  if (launch_pdl(qg::w4a8_prepare_activations, (int)M, 256, 0, s, reinterpret_cast<const uint2*>(A),
-                 reinterpret_cast<uint2*>(a_prepared), row_sums, reinterpret_cast<uint32_t*>(ws),
-                 (int)(kW4CounterBytes / 4), (int)K))
+  if (X != nullptr) {
+    if (launch_pdl(qg::w4a8_quant_prepare_activations, (int)M, 256, 0, s, static_cast<const uint4*>(X), x_is_bf16,
+                   round_scale, reinterpret_cast<uint2*>(a_prepared), row_sums, scale_out,
+                   reinterpret_cast<uint32_t*>(ws), (int)(kW4CounterBytes / 4), (int)K))
+      return -1;
+  } else if (launch_pdl(qg::w4a8_prepare_activations, (int)M, 256, 0, s, reinterpret_cast<const uint2*>(A),
+                        reinterpret_cast<uint2*>(a_prepared), row_sums, reinterpret_cast<uint32_t*>(ws),
+                        (int)(kW4CounterBytes / 4), (int)K))
     return -1;
   const bool sgn = signed_nibbles != 0;
   switch (mt) {
@@ -392,7 +400,7 @@ static int w4a8_fused(const int8_t* A, const uint8_t* qB, int8_t* workspace, int
 
 extern "C" {
 
-int qgemm_version(void) { return 1005; }  // 1.5: + group-sum W4A16 kernel, gathered W4A16 (peer stores), IPC helpers
+int qgemm_version(void) { return 1006; }  // 1.6: + in-flight zero tensors, W4A8 with the activation quantiser fused into its pre-pass
 
 const char* qgemm_last_error(void) { return g_err; }
 
@@ -1002,6 +1010,23 @@ int qgemm_w4a8(const int8_t* A, const uint8_t* qB, int8_t* workspace, void* C, i
   if (out_dtype == QGEMM_DT_I32)
     return qgemm_w8a8(A, workspace, nullptr, nullptr, C, nullptr, 1, M, N, K, 1, 0, QGEMM_DT_I32, QGEMM_B_NK, status, stream);
   return fail("qgemm_w4a8: out_dtype must be I32; cast the result on the caller's side (got %d)", out_dtype);
+}
+
+int qgemm_w4a8_act_quant(const void* X, int x_dtype, const uint8_t* qB, int8_t* workspace, int32_t* C, float* scale_a,
+                         int round_scale, int64_t M, int64_t N, int64_t K, int signed_nibbles, uint32_t* status,
+                         void* stream) {
+  if (X == nullptr || qB == nullptr || workspace == nullptr || C == nullptr || scale_a == nullptr)
+    return fail("qgemm_w4a8_act_quant: X, qB, workspace, C and scale_a must not be null");
+  if (x_dtype != QGEMM_DT_F16 && x_dtype != QGEMM_DT_BF16) return fail("qgemm_w4a8_act_quant: x_dtype must be F16 or BF16 (got %d)", x_dtype);
+  if (M <= 0 || N <= 0 || K <= 0) return fail("qgemm_w4a8_act_quant: M, N, K must be positive (got %lld, %lld, %lld)", (long long)M, (long long)N, (long long)K);
+  if (K % 32 != 0 || N % 16 != 0) return fail("qgemm_w4a8_act_quant: K must be a multiple of 32 and N of 16 (got K=%lld, N=%lld)", (long long)K, (long long)N);
+  if (!aligned16(X) || !aligned16(qB) || !aligned16(C) || !aligned16(workspace)) return fail("qgemm_w4a8_act_quant: pointers must be 16-byte aligned");
+  if (M > 128)
+    return fail("qgemm_w4a8_act_quant: the fused form covers M <= 128 (got %lld); use qgemm_act_quant and qgemm_w4a8 above that", (long long)M);
+  const int rc = w4a8_fused(nullptr, qB, workspace, C, M, N, K, signed_nibbles, status, static_cast<cudaStream_t>(stream), X,
+                            x_dtype == QGEMM_DT_BF16 ? 1 : 0, round_scale, scale_a);
+  if (rc > 0) return fail("qgemm_w4a8_act_quant: the [N, K] workspace is too small for the kernel's scratch (N * K = %lld bytes)", (long long)(N * K));
+  return rc;
 }
 
 }  // extern "C"

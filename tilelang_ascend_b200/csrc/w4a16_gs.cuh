@@ -162,6 +162,20 @@ __device__ __forceinline__ bool w4g_elect_one() {
 __device__ __forceinline__ void w4g_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// Two fp32 FMAs in one instruction (d0 += a0 * s, d1 += a1 * s), each rounded exactly like fmaf: the drain warps'
+// instruction streams are serial chains, so halving their FMA count shortens the chain.
+__device__ __forceinline__ void w4g_fma2(float& d0, float& d1, uint32_t a0, uint32_t a1, float s) {
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rc;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %4};\n\t"
+      "mov.b64 rc, {%0, %1};\n\t"
+      "fma.rn.f32x2 rc, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rc;\n\t"
+      "}"
+      : "+f"(d0), "+f"(d1)
+      : "r"(a0), "r"(a1), "f"(s));
+}
 // Named barrier of the eight drain warps.
 __device__ __forceinline__ void w4g_epi_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
@@ -448,9 +462,9 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
           __syncwarp();
           if (lead) w4g_arrive<W4G_ACC_EMPTY>(bs);
 #pragma unroll
-          for (int m = 0; m < 16; ++m) {
-            psum[m] = fmaf(__uint_as_float(r[m]), s0, psum[m]);
-            psum[m] = fmaf(__uint_as_float(r[16 + m]), s1, psum[m]);
+          for (int m = 0; m < 16; m += 2) {
+            w4g_fma2(psum[m], psum[m + 1], r[m], r[m + 1], s0);
+            w4g_fma2(psum[m], psum[m + 1], r[16 + m], r[17 + m], s1);
           }
         } else {
 #pragma unroll
@@ -465,7 +479,12 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             }
             const float s = (c4 >> 1) ? s1 : s0;
 #pragma unroll
-            for (int m = 0; m < 16; ++m) psum[16 * (c4 & 1) + m] = fmaf(__uint_as_float(r[m]), s, psum[16 * (c4 & 1) + m]);
+            if constexpr (MT == 64) {  // the paired form costs this tile registers it does not have (spills)
+              for (int m = 0; m < 16; ++m) psum[16 * (c4 & 1) + m] = fmaf(__uint_as_float(r[m]), s, psum[16 * (c4 & 1) + m]);
+            } else {
+              for (int m = 0; m < 16; m += 2)
+                w4g_fma2(psum[16 * (c4 & 1) + m], psum[16 * (c4 & 1) + m + 1], r[m], r[m + 1], s);
+            }
           }
         }
       }

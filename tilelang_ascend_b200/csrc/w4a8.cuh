@@ -9,6 +9,7 @@
 // weights, which leaves the kernel bound by the weight stream.
 #pragma once
 
+#include "act_quant.cuh"
 #include "common.cuh"
 #include "w4a16.cuh"
 
@@ -75,6 +76,75 @@ w4a8_prepare_activations(const uint2* __restrict__ in, uint2* __restrict__ out, 
     int s = 0;
     for (int w = 0; w < 8; ++w) s += red[w];
     row_sums[m] = s;
+  }
+}
+
+// The same pre-pass with the per-token activation quantiser in front of it, fused: bf16 / f16 activations [M, K] ->
+// scale[m] = max(amax, 1e-4) / 127 (optionally rounded up to a power of two), int8 values rint(x / scale) written
+// straight in the kernel's byte order, and their row sums.  The arithmetic is act_quant_kernel's (act_quant.cuh),
+// so the int8 values and scales are bit-identical to running that kernel first
+// (examples/deepseek_v4/act_quant.py:112-142); what disappears is one launch and the int8 round trip through
+// memory.  One block per row; a thread keeps up to eight 16-byte chunks of the row in registers between the abs-max
+// pass and the quantise pass (K <= 16384), longer rows are read again.
+__global__ void __launch_bounds__(256)
+w4a8_quant_prepare_activations(const uint4* __restrict__ X, int is_bf16, int round_scale, uint2* __restrict__ out,
+                               int* __restrict__ row_sums, float* __restrict__ scales, uint32_t* __restrict__ counters,
+                               int n_counters, int K) {
+  __shared__ float redf[8];
+  __shared__ int red[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_counters; i += gridDim.x * blockDim.x) counters[i] = 0u;
+  const int m = blockIdx.x;
+  const int chunks = K >> 3;
+  const bool bf16 = is_bf16 != 0;
+  const uint4* x = X + (size_t)m * chunks;
+  uint2* dst = out + (size_t)m * chunks;
+  constexpr int KEEP = 8;
+  uint4 keep[KEEP];
+  uint32_t m2 = 0u;
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < chunks) {
+      keep[i] = __ldg(x + c);
+      m2 = aq_absmax8(keep[i], bf16, m2);
+    }
+  }
+  for (int c = threadIdx.x + KEEP * 256; c < chunks; c += 256) m2 = aq_absmax8(__ldg(x + c), bf16, m2);
+  float mx = aq_pair_max(m2, bf16);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) redf[threadIdx.x >> 5] = mx;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < 8; ++w) mx = fmaxf(mx, redf[w]);
+  const float amax = fmaxf(mx, 1e-4f);
+  float scale = __fdiv_rn(amax, 127.0f);
+  if (round_scale) scale = aq_pow2_ceil(scale);
+  const float rcp = __frcp_rn(scale);
+  int acc = 0;
+  auto emit = [&](int c, const uint4& v) {
+    const uint2 q = aq_quant8(v, bf16, scale, rcp);  // eight int8 values in K order
+    acc = __dp4a((int)q.x, 0x01010101, acc);
+    acc = __dp4a((int)q.y, 0x01010101, acc);
+    dst[c] = make_uint2(__byte_perm(q.x, q.y, 0x6420), __byte_perm(q.x, q.y, 0x7531));
+  };
+#pragma unroll
+  for (int i = 0; i < KEEP; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < chunks) emit(c, keep[i]);
+  }
+  for (int c = threadIdx.x + KEEP * 256; c < chunks; c += 256) emit(c, __ldg(x + c));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int sum = 0;
+    for (int w = 0; w < 8; ++w) sum += red[w];
+    row_sums[m] = sum;
+    scales[m] = scale;
   }
 }
 

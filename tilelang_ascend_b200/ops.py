@@ -485,6 +485,36 @@ def w4a8_gemm_cv(M: int, N: int, K: int):
 
 
 @functools.lru_cache(maxsize=None)
+def w4a8_gemm_act_quant(M: int, N: int, K: int, round_scale: bool = False):
+    """The per-token activation quantiser (examples/deepseek_v4/act_quant.py:33-92) fused into the W4A8 operator
+    (examples/dequantize_gemm/example_dequant_gemm_w4a8.py:26) for up to 128 tokens.
+
+    Returns ``kernel(X[M,K] bf16/f16, qB[N,K/2] uint8, workspace[N,K] int8, C[M,N] int32) -> (C, scale_a[M] fp32)``
+    with ``C`` and ``scale_a`` bit-identical to ``act_quant`` followed by ``w4a8_gemm_cv``; the dequantised product is
+    ``C * scale_a[:, None] * weight_scale``."""
+
+    def kernel(X, qB, workspace, C, stream=None, status=None):
+        lib = _lib.load()
+        _require_cuda(X, "X")
+        dev = X.device
+        if X.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError(f"Buffer dtype mismatch for parameter X: expected float16 or bfloat16, got {X.dtype}")
+        _check_tensor(X, 0, "X", X.dtype, (M, K), dev)
+        _check_tensor(qB, 1, "qB", torch.uint8, (N, K // 2), dev)
+        _check_tensor(workspace, 2, "workspace", torch.int8, (N, K), dev)
+        _check_tensor(C, 3, "C", torch.int32, (M, N), dev)
+        scale_a = torch.empty((M,), dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            rc = lib.qgemm_w4a8_act_quant(X.data_ptr(), _ABI_DT[X.dtype], qB.data_ptr(), workspace.data_ptr(), C.data_ptr(),
+                                          scale_a.data_ptr(), 1 if round_scale else 0, M, N, K, 1, _ptr(status),
+                                          _stream_handle(stream, dev))
+        _lib.check(rc, "qgemm_w4a8_act_quant")
+        return C, scale_a
+
+    return kernel
+
+
+@functools.lru_cache(maxsize=None)
 def dequant_gemm_int8_wrapper(M: int, N: int, K: int, block_M: int, block_N: int, block_K: int,
                               output_dtype: str = "int32"):
     """Factory with the signature of examples/dequantize_gemm/example_dequant_gemm_fine_grained.py:226-234.
