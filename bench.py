@@ -39,7 +39,7 @@ CFG2 = dict(M=16, K=4096, N=4096, group=128)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the committed ncu
 # summary under profiles/.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 295446016  # profiles/w4a16_gs_cfg2_headline.md (283.9 MB read + 11.6 MB written)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 293437952  # profiles/w4a16_gs_cfg2_headline.md (284.0 MB read + 9.5 MB written)
 
 
 def w4a16_bytes(M, K, N, group, out_bytes=2, a_bytes=2):
@@ -636,6 +636,10 @@ def run_case(args):
             Sb = S.unsqueeze(0).repeat(args.batch, 1, 1).contiguous()
             for i in range(n):
                 C = q.w4a16_gemm(Ab, Pb, Sb, 8, 128)
+        elif args.zeros:  # a zeros tensor [K/g, N] of integer zero points (zero mode "quantized")
+            Z = torch.randint(0, 16, tuple(S.shape), generator=torch.Generator().manual_seed(9)).to(torch.float16).cuda()
+            for i in range(n):
+                C = q.w4a16_gemm(A, Ps[i % sets], S, Z, 128, zeros_mode="quantized")
         else:
             for i in range(n):
                 C = q.w4a16_gemm(A, Ps[i % sets], S, 8, 128)
@@ -670,6 +674,7 @@ def main():
     ap.add_argument("--m", type=int, default=None)
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--zeros", action="store_true", help="with --case cfg2|cfg5: per-group zero points from a zeros tensor")
     args = ap.parse_args()
     if args.case is not None:
         return run_case(args)
