@@ -43,6 +43,7 @@ extern "C" {
 #define QGEMM_ST_TIMEOUT_EPILOGUE 3
 #define QGEMM_ST_TIMEOUT_DEQUANT 4
 #define QGEMM_ST_TIMEOUT_DRAIN 5
+#define QGEMM_ST_TIMEOUT_PEER 6      /* qgemm_peer_signal_wait: a peer's signal did not arrive within the wait limit */
 
 /* Library version (major * 1000 + minor). */
 int qgemm_version(void);
@@ -226,6 +227,25 @@ int qgemm_w4a16_gather(const void* A, const uint8_t* B_packed, const void* scale
 int qgemm_ipc_export(const void* dev_ptr, void* handle_out, int64_t* offset_out);
 int qgemm_ipc_open(const void* handle, void** base_out);
 int qgemm_ipc_close(void* base);
+
+/*
+ * "Everything I stored into your buffers has landed" between the ranks of the gathered form, without a collective:
+ * every rank owns an array of n 32-bit flags (zero-initialised, mapped into all processes like the output buffers);
+ * the call stores `epoch` into slot [this rank] of every rank's array (flag_slots[r] = that slot's address in rank
+ * r's array, this rank's own included) and then waits until all n slots of its own array (`local_flags`) have reached
+ * `epoch` (compared modulo 2^32, so epochs only have to increase by one from call to call).  With `epoch_counter`
+ * non-null the epoch is instead that device word (owned by this rank, zero-initialised) incremented by the kernel
+ * itself, so that a launch captured in a CUDA graph keeps counting when the graph is replayed; every rank must then
+ * execute the same sequence of calls.  One tiny kernel in
+ * stream order behind the GEMM launch: the stores of that launch are visible to a peer before the flag is, and the
+ * peer's later kernels on its stream run after its own wait.  The wait is bounded by qgemm_set_wait_limit_ms; when it
+ * runs out, QGEMM_ST_TIMEOUT_PEER is stored in `status` and the kernel returns.  Replaces the one-element all-reduce
+ * that otherwise serves as this barrier (about 12 us at decode sizes).  Ranks must be on different GPUs.
+ * No reference counterpart (the reference's analogue is the signal of its one-sided put,
+ * src/tl_templates/ascend/common.h:358-408).
+ */
+int qgemm_peer_signal_wait(void* const* flag_slots, int n, const uint32_t* local_flags, uint32_t epoch,
+                           uint32_t* epoch_counter, uint32_t* status, void* stream);
 
 /*
  * W4A16 dequantize-GEMM that needs no memory from the caller beyond inputs and output.  (No counterpart

@@ -47,6 +47,31 @@ def _worker(rank, world, port, q):
             loc = peer.forward(A.cuda(), gather=False)
             if not torch.equal(loc, out[:, peer.n0:peer.n1]):
                 ok, msg = False, f"M={M}: local block differs from the gathered columns"
+        # the all-reduce form of the "landed" barrier gives the same bits
+        peer_ar = ColumnShardedW4A16(P, S, 8, 128, peer_stores=True, landed="allreduce").to("cuda")
+        A, _, _ = oc.make_w4a16_inputs(16, K, N, "float16", 128, seed=116)
+        if not torch.equal(peer_ar(A.cuda()), peer(A.cuda())):
+            ok, msg = False, "flag-based and all-reduce-based forms differ"
+        peer_ar.close()
+        # replays of a captured graph keep their cross-rank ordering (the epoch is counted on the device): different
+        # activations per replay through one static input, every replay's result checked
+        static_A = A.cuda().clone()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            peer(static_A)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                # a result stays valid until the forward after next: keep private copies, made in stream order
+                outs = [peer(static_A).clone() for _ in range(4)]
+            for rep in range(3):
+                Ar, _, _ = oc.make_w4a16_inputs(16, K, N, "float16", 128, seed=200 + rep)
+                static_A.copy_(Ar.cuda())
+                graph.replay()
+                side.synchronize()
+                ref = oc.dequant_gemm_fp16_ref(Ar, P, "float16", S, 8, 128)
+                if not all(torch.allclose(o.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2) for o in outs):
+                    ok, msg = False, f"graph replay {rep}: gathered output differs from the oracle"
         peer.close()
         dist.barrier()
         dist.destroy_process_group()
@@ -70,3 +95,32 @@ def test_column_sharded_peer_stores_match_oracle_and_collective():
     for p in procs:
         p.join(timeout=60)
     assert all(ok for _, ok, _ in res), res
+
+
+def test_peer_signal_wait_gives_up_cleanly_when_a_peer_never_signals():
+    """The bounded wait of the "landed" kernel, made to expire in the safe way: a flag array with a slot that nothing
+    ever sets.  The kernel must return by itself after the limit (20 ms here) with QGEMM_ST_TIMEOUT_PEER in the status
+    word, and the context must stay usable.  One GPU, no peer involved."""
+    import tilelang_ascend_b200 as q
+    from tilelang_ascend_b200 import _lib
+    from tilelang_ascend_b200.ops import peer_signal_wait
+    lib = _lib.load()
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    me = flags.data_ptr()  # both "ranks" signal into slot 0; slot 1 is never written
+    try:
+        lib.qgemm_set_wait_limit_ms(20)
+        peer_signal_wait([me, me], flags, epoch=1, status=status)
+        torch.cuda.synchronize()
+    finally:
+        lib.qgemm_set_wait_limit_ms(2000)
+    assert int(status.item()) == 6  # QGEMM_ST_TIMEOUT_PEER
+    assert int(flags[0].item()) == 1 and int(flags[1].item()) == 0
+    # a satisfied wait returns without touching the status, and the device-side epoch counter counts
+    status.zero_()
+    flags[1] = 5
+    peer_signal_wait([me, me + 4], flags, epoch_counter=flags[32:33], status=status)  # epoch 1: both slots >= 1
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(flags[32].item()) == 1
+    x = torch.ones(8, device="cuda")
+    assert float((x * 2).sum().item()) == 16.0

@@ -19,7 +19,8 @@ DT_F16, DT_BF16, DT_I32 = 0, 1, 2
 B_KN, B_NK = 0, 1
 
 STATUS_NAMES = {0: "ok", 1: "timeout in TMA producer", 2: "timeout in MMA issuer", 3: "timeout in epilogue",
-                4: "timeout in dequant warps", 5: "timeout while draining copies"}
+                4: "timeout in dequant warps", 5: "timeout while draining copies",
+                6: "a peer's signal did not arrive"}
 
 # name -> (restype, argtypes); must list every symbol that include/qgemm.h declares.
 _c = ctypes
@@ -54,6 +55,8 @@ SIGNATURES = {
     "qgemm_ipc_export": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p]),
     "qgemm_ipc_open": (_c.c_int, [_c.c_void_p, _c.c_void_p]),
     "qgemm_ipc_close": (_c.c_int, [_c.c_void_p]),
+    "qgemm_peer_signal_wait": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p, _c.c_uint32, _c.c_void_p, _c.c_void_p,
+                                          _c.c_void_p]),
     "qgemm_w4a16_noalloc": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p,
                                        _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_void_p,
                                        _c.c_void_p]),

@@ -23,6 +23,7 @@ enum : uint32_t {
   ST_TIMEOUT_EPILOGUE = 3,
   ST_TIMEOUT_DEQUANT = 4,
   ST_TIMEOUT_DRAIN = 5,
+  ST_TIMEOUT_PEER = 6,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -898,6 +898,61 @@ int qgemm_w4a16_gather(const void* A, const uint8_t* B_packed, const void* scale
                     status, stream, nullptr, QGEMM_ZERO_ORIGINAL, QGEMM_W4_SEQUENTIAL, &gd);
 }
 
+}  // extern "C"
+
+// ---- "my blocks have landed" between the ranks of the gathered form ----
+namespace {
+struct PeerSlots {
+  uint32_t* slot[8];
+};
+// Thread r: release-store the epoch into this rank's slot of rank r's flag array, then acquire-poll slot r of this
+// rank's own array until rank r's epoch has arrived.  Bounded: gives up after limit_ns and reports it.
+__global__ void peer_signal_wait_kernel(PeerSlots dst, const uint32_t* local_flags, int n, uint32_t epoch,
+                                        uint32_t* epoch_counter, unsigned long long limit_ns, uint32_t* status) {
+  __shared__ uint32_t epoch_s;
+  const int r = threadIdx.x;
+  if (epoch_counter != nullptr) {  // the epoch lives on the device: replays of a captured launch keep counting
+    if (r == 0) {
+      epoch_s = *epoch_counter + 1u;
+      *epoch_counter = epoch_s;
+    }
+    __syncthreads();
+    epoch = epoch_s;
+  }
+  if (r >= n) return;
+  __threadfence_system();
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst.slot[r]), "r"(epoch) : "memory");
+  const uint32_t* mine = local_flags + r;
+  const unsigned long long t0 = qg::global_timer_ns();
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int32_t)(v - epoch) >= 0) break;
+    if (qg::global_timer_ns() - t0 > limit_ns) {
+      if (status != nullptr) atomicMax(status, (uint32_t)qg::ST_TIMEOUT_PEER);
+      break;
+    }
+    __nanosleep(100);
+  }
+}
+}  // namespace
+
+extern "C" {
+
+int qgemm_peer_signal_wait(void* const* flag_slots, int n, const uint32_t* local_flags, uint32_t epoch,
+                           uint32_t* epoch_counter, uint32_t* status, void* stream) {
+  if (flag_slots == nullptr || local_flags == nullptr || n < 1 || n > 8) return fail("qgemm_peer_signal_wait: 1 to 8 ranks, non-null flag arrays required (got n=%d)", n);
+  PeerSlots dst;
+  for (int r = 0; r < 8; ++r) dst.slot[r] = nullptr;
+  for (int r = 0; r < n; ++r) {
+    if (flag_slots[r] == nullptr || (reinterpret_cast<uintptr_t>(flag_slots[r]) & 3u) != 0) return fail("qgemm_peer_signal_wait: flag slot %d is null or misaligned", r);
+    dst.slot[r] = static_cast<uint32_t*>(flag_slots[r]);
+  }
+  peer_signal_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(dst, local_flags, n, epoch, epoch_counter, g_wait_limit_ns, status);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 // ---- mapping another process's buffer into this one (same node), for the gathered form ----
 static_assert(sizeof(cudaIpcMemHandle_t) == QGEMM_IPC_HANDLE_BYTES, "IPC handle size");
 

@@ -55,15 +55,17 @@ class ColumnShardedW4A16:
     * peer stores (CUDA ranks of one node, the default there): every rank owns a full ``[M, N]`` buffer, the
       buffers are mapped into all processes once per token count, and the GEMM kernel's epilogue writes this
       rank's column block into every rank's buffer itself.  The output crosses NVLink while the GEMM still runs,
-      nothing is re-arranged afterwards, and the only collective left is a one-element all-reduce that tells a
-      rank when all blocks have landed.  Two buffers alternate, so a rank may still read one result while its
-      peers already write the next.
+      nothing is re-arranged afterwards.  What tells a rank that all blocks have landed is a flag per peer in a
+      small mapped array, set and awaited by one tiny kernel behind the GEMM (``landed="flags"``, the default), or
+      a one-element all-reduce (``landed="allreduce"``).  Two buffers alternate, so a rank may still read one
+      result while its peers already write the next: a returned tensor stays valid until the forward after next
+      of the same token count (copy it in stream order to keep it longer).
     * collective (``peer_stores=False``, CPU / gloo, or when mapping fails): one all-gather of the ``[M, N/g]``
       blocks and a copy into column order (no copy for a single token, whose blocks are already in order)."""
 
     def __init__(self, B_packed: torch.Tensor, scales: Optional[torch.Tensor], zero: int = 8, group_size: int = 128,
                  group: Optional[dist.ProcessGroup] = None, gemm: Optional[Callable] = None, multiple: int = 128,
-                 peer_stores="auto", share_buffers_with: Optional["ColumnShardedW4A16"] = None):
+                 peer_stores="auto", share_buffers_with: Optional["ColumnShardedW4A16"] = None, landed: str = "flags"):
         self.pg = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -82,7 +84,11 @@ class ColumnShardedW4A16:
         self._peers = {}    # (M, dtype) -> [generation 0, generation 1], each (own buffer, [address per rank])
         self._gen = {}
         self._opened = []   # (base address, device) of every mapping of a peer's allocation
-        self._token = None  # one element, all-reduced as the "all blocks have landed" barrier
+        if landed not in ("flags", "allreduce"):
+            raise ValueError("landed must be 'flags' or 'allreduce'")
+        self.landed = landed
+        self._token = None  # one element, all-reduced as the "all blocks have landed" barrier (landed="allreduce")
+        self._flags = None  # (own int32 flag array, [address of this rank's slot in every rank's array])
         self._owner = self  # the layer whose output buffers this one writes (several layers of one shape, say the
         if share_buffers_with is not None:  # same projection of different blocks, can share them)
             if share_buffers_with.N != self.N or share_buffers_with.world != self.world:
@@ -125,6 +131,20 @@ class ColumnShardedW4A16:
             self._gen[key] = 0
             if self._token is None:
                 self._token = torch.zeros(1, dtype=torch.float32, device=device)
+            if self._flags is None and self.landed == "flags":
+                flags = torch.zeros(64, dtype=torch.int32, device=device)  # a slot per rank; the rest pads the line
+                infos = [None] * self.world
+                dist.all_gather_object(infos, ipc_export(flags), group=self.pg)
+                slots = []
+                for r, (handle, off) in enumerate(infos):
+                    if r == self.rank:
+                        slots.append(flags.data_ptr() + 4 * self.rank)
+                    else:
+                        base = ipc_open(handle, device)
+                        self._opened.append((base, device))
+                        slots.append(base + off + 4 * self.rank)
+                self._flags = (flags, slots)
+                torch.cuda.synchronize(device)  # the flags are zero before any peer can signal
             dist.barrier(group=self.pg)  # every rank has mapped every buffer before anyone writes
         return key
 
@@ -138,6 +158,7 @@ class ColumnShardedW4A16:
                 ipc_close(base, device)
             self._opened = []
             self._peers = {}
+            self._flags = None
 
     # ---------------------------------------------------------------- forward
     def forward(self, A: torch.Tensor, gather: bool = True) -> torch.Tensor:
@@ -157,7 +178,13 @@ class ColumnShardedW4A16:
                 own._gen[key] = g ^ 1
                 buf, ptrs = own._peers[key][g]
                 w4a16_gemm_gather(A, self.B_local, self.s_local, self.zero, self.group_size, ptrs, self.N, self.n0)
-                dist.all_reduce(own._token, group=self.pg)  # in stream order behind the kernel: all blocks have landed
+                # in stream order behind the kernel: all ranks' blocks have landed in this rank's buffer
+                if own._flags is not None:
+                    from .ops import peer_signal_wait
+                    # the epoch is counted on the device (slot 32 of the flag array), so graph replays keep counting
+                    peer_signal_wait(own._flags[1], own._flags[0], epoch_counter=own._flags[0][32:33])
+                else:
+                    dist.all_reduce(own._token, group=self.pg)
                 return buf
         C_local = self._gemm(A, self.B_local, self.s_local, self.zero, self.group_size)
         if not gather or self.world == 1:

@@ -359,6 +359,27 @@ def ipc_export(t: torch.Tensor):
     return bytes(handle), int(off.value)
 
 
+def peer_signal_wait(flag_slots, local_flags: torch.Tensor, epoch: int = 0, epoch_counter: Optional[torch.Tensor] = None,
+                     stream=None, status=None):
+    """Store an epoch into this rank's slot of every rank's flag array (``flag_slots``: one device address per rank)
+    and wait, on the stream, until every slot of ``local_flags`` (int32 ``[ranks]``) has reached it: the stream-ordered
+    "all peers' blocks have landed" of the gathered W4A16 form without a collective.  The epoch is ``epoch`` or, with
+    ``epoch_counter`` (an int32 CUDA tensor of one element that the kernel increments), counted on the device, which
+    keeps counting when a captured graph is replayed.  The wait is bounded (``qgemm_set_wait_limit_ms``); ``status``
+    receives QGEMM_ST_TIMEOUT_PEER if it runs out."""
+    import ctypes
+    lib = _lib.load()
+    n = len(flag_slots)
+    arr = (ctypes.c_void_p * n)(*[int(p) for p in flag_slots])
+    dev = local_flags.device
+    if local_flags.dtype != torch.int32 or local_flags.numel() < n or not local_flags.is_cuda:
+        raise ValueError("local_flags must be a CUDA int32 tensor with one element per rank")
+    with torch.cuda.device(dev):
+        rc = lib.qgemm_peer_signal_wait(ctypes.cast(arr, ctypes.c_void_p), n, local_flags.data_ptr(), int(epoch) & 0xFFFFFFFF,
+                                        _ptr(epoch_counter), _ptr(status), _stream_handle(stream, dev))
+    _lib.check(rc, "qgemm_peer_signal_wait")
+
+
 _ipc_mappings = {}  # (device index, handle) -> [base address, users]: an allocation is mapped once per process
 
 
