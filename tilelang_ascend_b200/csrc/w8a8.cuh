@@ -22,6 +22,8 @@ struct W8A8Params {
   int sb_mode;  // 0: one value for all; 1: [N]; 2: [batch, N]
   int sa_mode;  // 0: none; 1: [M]; 2: [batch, M]
   int m_tiles, n_tiles, num_tiles, k_blocks;
+  int group_m;  // tile rasterisation: the tiles of `group_m` row blocks are walked column block by column block
+
   int bn;            // columns per tile actually computed: a multiple of 32, at most the kernel's BN
   uint32_t* status;  // nullable device word
   unsigned long long wait_limit_ns;
@@ -53,7 +55,6 @@ constexpr int W8_BM = 128;      // tile rows (= MMA M, one TMEM lane per row)
 constexpr int W8_BK = 128;      // K bytes per pipeline stage (one 128-byte swizzle atom)
 constexpr int W8_UMMA_K = 32;   // K per tcgen05.mma for 8-bit operands
 constexpr int W8_THREADS = 192;
-constexpr int W8_GROUP_M = 8;   // tile rasterisation: walk 8 row-tiles per column-tile band
 
 template <int BN>
 struct W8Cfg {
@@ -72,10 +73,10 @@ __device__ __forceinline__ void w8_decode_tile(const W8A8Params& p, int tile, in
   const int per_batch = p.m_tiles * p.n_tiles;
   b = tile / per_batch;
   const int r = tile - b * per_batch;
-  const int band = W8_GROUP_M * p.n_tiles;
+  const int band = p.group_m * p.n_tiles;
   const int g = r / band;
-  const int first_m = g * W8_GROUP_M;
-  const int gsz = min(p.m_tiles - first_m, W8_GROUP_M);
+  const int first_m = g * p.group_m;
+  const int gsz = min(p.m_tiles - first_m, p.group_m);
   const int in_band = r - g * band;
   m_blk = first_m + in_band % gsz;
   n_blk = in_band / gsz;
@@ -279,6 +280,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // accumulators (the loads hide behind the main loop), and keeps the next 32-column chunk's tcgen05.ld in
     // flight while it converts and stores the current one.
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const uint64_t pol_out = l2_policy_evict_first();  // the output is written once and not read here
     float* sb_s = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + Cfg::BAR_BYTES) + q * BN;
     uint8_t* my_stage = out_stage + q * 4096;  // [32 rows][128 B], 16-byte piece j of row r at (j ^ (r & 7))
     int it = 0;
@@ -453,9 +455,10 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           __syncwarp();
           if (lane == 0) {
             if (p.n_dst == 0) {
-              tma_store_3d(&tmC, my_stage, t.n0 + c2 * 32, t.m0 + q * 32, t.bA);
+              tma_store_3d_hint(&tmC, my_stage, t.n0 + c2 * 32, t.m0 + q * 32, t.bA, pol_out);
             } else {
-              for (int d = 0; d < p.n_dst; ++d) tma_store_3d(&tmCs.m[d], my_stage, p.col0 + t.n0 + c2 * 32, t.m0 + q * 32, 0);
+              for (int d = 0; d < p.n_dst; ++d)
+                tma_store_3d_hint(&tmCs.m[d], my_stage, p.col0 + t.n0 + c2 * 32, t.m0 + q * 32, 0, pol_out);
             }
             bulk_commit_group();
           }
