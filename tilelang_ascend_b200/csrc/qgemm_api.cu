@@ -177,10 +177,12 @@ int launch_pdl(void (*kernel)(KArgs...), int grid, int threads, int smem, cudaSt
 
 // Rasterisation band: the tiles of `group_m` consecutive row blocks are walked column block by column block, so a
 // wave of CTAs shares few B tiles and the band's A rows (group_m x 128 x K bytes) stay in L2 while every B tile
-// streams through once per band.  As many row blocks as keep the band's A rows within 20 MB (config 3: all 32 row
-// blocks, 16.8 MB, B read from DRAM once instead of four times: 171 -> 165 us), at least 8.
+// streams through once per band.  As many row blocks as keep the band's A rows within 34 MB, at least 8: config 3
+// takes all 32 row blocks (16.8 MB, B read from DRAM once instead of four times: 172 -> 165 us; 16 or 24 row blocks:
+// 170 us), the f16 GEMM of 4096 x 8192 x 28672 takes 16 (33.5 MB: 1525 us; 8: 1570, 32: 1553).
 int w8_group_m(int64_t m_tiles, int64_t k_bytes) {
-  int64_t g = (20ll << 20) / (128 * (k_bytes > 0 ? k_bytes : 1));
+  static const int forced = getenv("QGEMM_W8_GROUP_M") ? atoi(getenv("QGEMM_W8_GROUP_M")) : 0;  // tuning override
+  int64_t g = forced > 0 ? forced : (34ll << 20) / (128 * (k_bytes > 0 ? k_bytes : 1));
   if (g < 8) g = 8;
   if (g > m_tiles) g = m_tiles;
   return (int)(g > 0 ? g : 1);
