@@ -546,7 +546,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       // Segment end.  The four epilogue warps decide together whether to go on (a warp that left alone would
       // leave the others waiting at the named barrier for ever): a wait that gave up set the abort flag before its
       // warp reached the barrier below; one thread reads the flag once and publishes it, with the split-K
-      // verdict, in a control word that alternates between two slots by segment, so that a fast warp's next
+      // outcome, in a control word that alternates between two slots by segment, so that a fast warp's next
       // write cannot overtake a slow warp's read.
       const int par = seg_idx & 1;
       ++seg_idx;

@@ -528,7 +528,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         }
       }
       // The eight drain warps decide together whether to go on: one thread reads the abort word once and
-      // publishes it (with the split-K verdict) in a control word that alternates between two slots, so a fast
+      // publishes it (with the split-K outcome) in a control word that alternates between two slots, so a fast
       // warp's next write cannot overtake a slow warp's read.
       w4g_epi_bar();
       if (warp == W4G_FIRST_EPI_WARP && lane == 0) {

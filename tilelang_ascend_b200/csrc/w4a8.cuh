@@ -400,7 +400,7 @@ w4a8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       }
       // Segment end.  The four epilogue warps decide together whether to go on (a warp that left alone would
       // leave the others waiting at the named barrier for ever): one thread reads the abort flag once and
-      // publishes it, with the split-K verdict, in a control word that alternates between two slots by segment.
+      // publishes it, with the split-K outcome, in a control word that alternates between two slots by segment.
       const int par = seg_idx & 1;
       ++seg_idx;
       const long long first_item = (long long)tile * p.KS;
