@@ -41,6 +41,9 @@ struct W4A16Params {
   int batch;            // independent problems of the same shape (A, B_packed, scales, C all carry a leading batch dimension)
   int m_tiles, n_tiles, num_tiles;  // num_tiles = batch * n_tiles * m_tiles; tile = (b * n_tiles + n_tile) * m_tiles + m_tile
   int KS;               // 256-wide K slabs per tile
+  // Group-sum kernel only: tiles 0 .. sk_tiles - 1 are cut stream-K fashion over all CTAs, then CTA c takes dp_rounds
+  // whole tiles sk_tiles + c + j * grid.  The other kernels deal all (tile, slab) items evenly (total_items).
+  int sk_tiles, dp_rounds;
   int scale_rows;       // scale rows fetched per slab (256 / group, at least 1)
   long long total_items;
   uint32_t* status;

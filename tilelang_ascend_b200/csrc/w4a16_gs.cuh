@@ -185,6 +185,22 @@ __device__ __forceinline__ uint32_t w4g_visit_parity(uint32_t c, int u) {
   return (PER == 4) ? (c & 1u) : (uint32_t)((u / PER) & 1);
 }
 
+// The segments of a CTA: those of its stream-K range, then its whole tiles (first_dp, first_dp + stride, ...).
+struct W4HybridIter {
+  W4SegIter sk;
+  int next_dp, dp_left, stride, KS;
+  __device__ __forceinline__ bool next(int& tile, int& ks0, int& ks1) {
+    if (sk.next(tile, ks0, ks1)) return true;
+    if (dp_left <= 0) return false;
+    tile = next_dp;
+    ks0 = 0;
+    ks1 = KS;
+    next_dp += stride;
+    --dp_left;
+    return true;
+  }
+};
+
 // GATHER = true is the gathered form (several destination buffers, see W4A16Params::c_dst); it is a separate
 // instantiation because the destination loop in the store path costs the plain kernel 8 % through register
 // allocation alone.
@@ -279,9 +295,14 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 
   const int G = gridDim.x;
   const int cta = blockIdx.x;
-  const long long T = p.total_items;
+  // Work split: the first p.sk_tiles tiles are cut stream-K fashion (their slabs dealt evenly to the CTAs as
+  // contiguous ranges, partial tiles meeting through the scratch buffer); after its range CTA c takes the whole tiles
+  // sk_tiles + c, sk_tiles + c + G, ...  The hand-overs of the partial tiles thus happen early, behind the following
+  // tiles' work, and the launch ends with plain tile writes.
+  const long long T = (long long)p.sk_tiles * p.KS;  // stream-K items
   const long long item0 = w4_range_begin(T, G, cta), item1 = w4_range_begin(T, G, cta + 1);
-  const int n_slabs = (int)(item1 - item0);  // this CTA's slabs, numbered 0.. in item order
+  const int n_sk = (int)(item1 - item0);
+  const int n_slabs = n_sk + p.dp_rounds * p.KS;  // this CTA's slabs, numbered 0.. in processing order
 
   if (warp <= 2) {
     // ------------------------------------------------------------------ TMA producers
@@ -292,8 +313,8 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       const uint32_t empty0 = bar0 + (warp == 0 ? W4G_RAW_EMPTY : (warp == 1 ? W4G_A_EMPTY : W4G_SC_EMPTY));
       const int depth = warp == 0 ? RS : (warp == 1 ? AS : SS);
       const uint32_t sc_tx = (uint32_t)p.scale_rows * 256u;
-      int tile = (int)(item0 / p.KS);
-      int ks = (int)(item0 - (long long)tile * p.KS);
+      int tile = n_sk > 0 ? (int)(item0 / p.KS) : p.sk_tiles + cta;
+      int ks = n_sk > 0 ? (int)(item0 - (long long)tile * p.KS) : 0;
       int b, n0, m0;
       w4_tile_coords(p, tile, MT, b, n0, m0);
       int st = 0;
@@ -323,9 +344,13 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         issued_mask |= 1u << st;
         parity_mask = (parity_mask & ~(1u << st)) | (phase << st);
         if (++st == depth) { st = 0; phase ^= 1u; }
-        if (++ks == p.KS) {
+        if (i + 1 == n_sk) {  // the stream-K range is done: on to this CTA's first whole tile
           ks = 0;
-          ++tile;
+          tile = p.sk_tiles + cta;
+          w4_tile_coords(p, tile, MT, b, n0, m0);
+        } else if (++ks == p.KS) {
+          ks = 0;
+          tile += (i + 1 < n_sk) ? 1 : G;
           w4_tile_coords(p, tile, MT, b, n0, m0);
         }
       }
@@ -417,7 +442,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     const bool scaled = p.has_scales != 0;
     const bool lead = lane == 0;
     pdl_wait();  // the arrival counters are zeroed by the pre-pass kernel in front of this one
-    W4SegIter seg{item0, item1, p.KS};
+    W4HybridIter seg{W4SegIter{item0, item1, p.KS}, p.sk_tiles + cta, p.dp_rounds, G, p.KS};
     int tile, ks0, ks1;
     uint32_t i_seg0 = 0;  // CTA-local index of the segment's first slab
     uint32_t fail = 0;
