@@ -166,9 +166,26 @@ def test_config3_full_size_properties():
     assert torch.equal(acc1 + acc2, acc)
 
 
-def test_two_cta_kernel_variant():
-    """The cta_group::2 form of the kernel (256 x 256 tile per CTA pair) is opt-in through QGEMM_W8_PAIR=1,
-    read once per process, so it is exercised in a child process: ragged M/N/K, both layouts, bit-exact."""
+SPLITK_SHAPES = [(0, 256, 4096, 1024), (2, 200, 4224, 528), (0, 130, 7168, 272), (3, 256, 4608, 1024)]
+
+
+@pytest.mark.parametrize("batch,M,K,N", SPLITK_SHAPES)
+def test_k_split_over_cta_pairs_is_exact(batch, M, K, N):
+    """Few tiles and a long K: the kernel runs in clusters of two CTAs that each accumulate half of K and exchange
+    halves of the tile through distributed shared memory.  Ragged M, N and K, both layouts: accumulators and outputs
+    bit-exact against the oracle."""
+    q = _q()
+    A, B, sa, sb = oc.make_w8a8_inputs(batch, M, K, N, seed=M + K)
+    ref, acc_ref = oc.quant_matmul_ref(A, B, sb, "bfloat16", scale_a=sa, return_acc=True)
+    C, acc = q.quant_matmul(A.cuda(), B.cuda(), sb.cuda(), scale_a=sa.cuda(), out_dtype="bfloat16", return_accumulators=True)
+    assert torch.equal(acc.cpu(), acc_ref) and torch.equal(C.cpu(), ref)
+    acc2 = q.quant_matmul(A.cuda(), B.transpose(-1, -2).contiguous().cuda(), None, out_dtype=torch.int32, b_layout="NK")
+    assert torch.equal(acc2.cpu(), acc_ref)
+
+
+def test_k_split_and_unsplit_kernels_give_the_same_bits():
+    """The same shapes with the K split switched off (QGEMM_W8_SPLITK=0 is read once per process, hence a child
+    process): identical outputs, which also shows that the shapes above really take the split path's place."""
     import os
     import subprocess
     import sys
@@ -176,19 +193,17 @@ def test_two_cta_kernel_variant():
 import torch
 from oracle import qgemm_oracle as oc
 import tilelang_ascend_b200 as q
-for batch, M, K, N in [(20, 300, 272, 528), (0, 2304, 528, 2320), (8, 1024, 1024, 1024)]:
-    A, B, sa, sb = oc.make_w8a8_inputs(batch, M, K, N, seed=M)
-    ref, acc_ref = oc.quant_matmul_ref(A, B, sb, "bfloat16", scale_a=sa, return_acc=True)
-    C, acc = q.quant_matmul(A.cuda(), B.cuda(), sb.cuda(), scale_a=sa.cuda(), out_dtype="bfloat16", return_accumulators=True)
-    assert torch.equal(acc.cpu(), acc_ref) and torch.equal(C.cpu(), ref), (batch, M, K, N)
-    acc2 = q.quant_matmul(A.cuda(), B.transpose(-1, -2).contiguous().cuda(), None, out_dtype=torch.int32, b_layout="NK")
-    assert torch.equal(acc2.cpu(), acc_ref), ("NK", batch, M, K, N)
-print("pair ok")
-"""
-    env = dict(os.environ, QGEMM_W8_PAIR="1")
+for batch, M, K, N in %r:
+    A, B, sa, sb = oc.make_w8a8_inputs(batch, M, K, N, seed=M + K)
+    ref = oc.quant_matmul_ref(A, B, sb, "bfloat16", scale_a=sa)
+    C = q.quant_matmul(A.cuda(), B.cuda(), sb.cuda(), scale_a=sa.cuda(), out_dtype="bfloat16")
+    assert torch.equal(C.cpu(), ref), (batch, M, K, N)
+print("unsplit ok")
+""" % (SPLITK_SHAPES,)
+    env = dict(os.environ, QGEMM_W8_SPLITK="0")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
-    assert r.returncode == 0 and "pair ok" in r.stdout, r.stdout + r.stderr
+    assert r.returncode == 0 and "unsplit ok" in r.stdout, r.stdout + r.stderr
 
 
 def test_rejects_bad_arguments():

@@ -468,9 +468,12 @@ static int w8a8_impl(const int8_t* A, const int8_t* B, const float* scale_b, con
   const int64_t m_tiles = meta ? num_blocks : (M + 127) / 128;
   const int64_t tiles256 = batchA * m_tiles * ((N + 255) / 256);
   // Fewer 256-wide tiles than half the SMs: split K over pairs of CTAs (one tile per pair, twice as many SMs at
-  // work on full-width tiles) instead of falling back to 128-wide tiles.  QGEMM_W8_SPLITK=0 disables it.
+  // work on full-width tiles) instead of falling back to 128-wide tiles - when K is long enough to pay for the
+  // cluster launch and the exchange: on 2 x 512 x K x 2048, split against 128-wide tiles, K = 7168: 19.8 / 23.6 us,
+  // 4096: 14.9 / 16.2, 3072: 13.7 / 13.3, and 256 x 1024 x 1024: 9.9 / 7.0, so the split starts at K = 4096.
+  // QGEMM_W8_SPLITK=0 disables it.
   static const int splitk_on = getenv("QGEMM_W8_SPLITK") ? atoi(getenv("QGEMM_W8_SPLITK")) : 1;
-  const bool use_splitk = splitk_on && meta == nullptr && N > 128 && 2 * tiles256 <= sms && (K + 127) / 128 >= 4;
+  const bool use_splitk = splitk_on && meta == nullptr && N > 128 && 2 * tiles256 <= sms && (K + 127) / 128 >= 32;
   const int BN = (N > 128 && (tiles256 >= sms || use_splitk)) ? 256 : 128;
   // Width actually computed per tile (a multiple of 32, at most BN).  Narrower tiles that fill the last
   // round of the persistent grid better were measured slower on B200 (224 instead of 256 columns on the

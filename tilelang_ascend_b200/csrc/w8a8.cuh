@@ -117,9 +117,11 @@ __device__ __forceinline__ W8Tile w8_tile(const W8A8Params& p, int item) {
 //
 // SPLITK = true is the form for grids that would leave more than half of the SMs idle (fewer 128 x 256 tiles than
 // half the SM count): the kernel is launched in clusters of two CTAs, one tile per cluster; each CTA accumulates
-// one half of the K range in its own tensor memory, CTA 1 then writes its int32 accumulators into CTA 0's shared
-// memory (the pipeline stages, idle by then) through distributed shared memory, and CTA 0 adds them in its
-// epilogue - an exact integer sum, so the result is bit-identical to the unsplit kernel's.  The counterpart in the
+// one half of the K range in its own tensor memory; then each CTA writes its int32 accumulators of the OTHER CTA's
+// half of the columns into that CTA's shared memory (the pipeline stages, idle by then) through distributed shared
+// memory, adds what it received to its own half and runs the epilogue for that half - an exact integer sum, so the
+// result is bit-identical to the unsplit kernel's, the exchange runs in both directions at once and each CTA
+// converts and stores half a tile.  The counterpart in the
 // reference is the K split of examples/gemm_splitk/example_tilelang_gemm_splitk.py:15-48, whose partial tiles meet
 // in global memory through atomic adds (src/tl_templates/ascend/common.h:249-259).
 template <int BN, bool B_NK, bool OUT_BF16, bool F16 = false, bool SPLITK = false>
@@ -140,8 +142,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tfull = bars + 2 * STAGES;
   uint64_t* tempty = tfull + 2;
   uint64_t* drain = tempty + 2;
-  uint64_t* stages_free = drain + 1;    // split form, in CTA 1: CTA 0's MMAs have finished reading its stages
-  uint64_t* partial_full = drain + 2;   // split form, in CTA 0: CTA 1's accumulators have arrived
+  uint64_t* stages_free = drain + 1;    // split form: the peer's MMAs have finished reading the peer's stages
+  uint64_t* partial_full = drain + 2;   // split form: the peer's accumulators for this CTA's columns have arrived
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 3);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -307,58 +309,60 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!mbar_wait_warp(&tfull[buf], tphase, ctl, ST_TIMEOUT_EPILOGUE)) break;
       tc_fence_after_sync();
+      // Split form: each CTA of the pair finishes ONE half of the tile's columns (CTA r: columns r * bn/2 ...): it sends
+      // its accumulators of the other half into the peer's pipeline stages and receives the peer's for its own, so
+      // that the exchange runs in both directions at once and each CTA converts and stores half a tile.
+      int c_begin = 0, c_end = t.bn >> 5;
       if constexpr (SPLITK) {
         const uint32_t taddr_s = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-        if (crank == 0) {
-          // this CTA's MMAs are done: its stages may be overwritten; then wait for the other half's sums
-          if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(stages_free), 1));
-          bool got = true;
-          if (lane == 0) {
-            const uint64_t t0 = global_timer_ns();
-            while (!mbar_try_wait_cluster(partial_full, 0)) {
-              if (*abort_flag || global_timer_ns() - t0 > p.wait_limit_ns) {
-                *abort_flag = 1u;
-                if (p.status) atomicMax(p.status, (uint32_t)ST_TIMEOUT_EPILOGUE);
-                got = false;
-                break;
-              }
+        const uint32_t peer = (uint32_t)(crank ^ 1);
+        const int half_chunks = t.bn >> 6;  // 32-column chunks per half
+        // this CTA's MMAs are done (tfull): the peer may write into its stages
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(stages_free), peer));
+        // ... and the peer's are done when its four epilogue warps have said so here
+        if (!mbar_wait_warp(stages_free, 0, ctl, ST_TIMEOUT_EPILOGUE)) break;
+        const uint32_t dst_row = mapa_u32(part_row, peer);
+#pragma unroll 1
+        for (int c = 0; c < half_chunks; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr_s + ((int)peer * half_chunks + c) * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj)
+            st_cluster_v4(dst_row + (uint32_t)((c * 8 + jj) * 128 * 16), r[4 * jj], r[4 * jj + 1], r[4 * jj + 2], r[4 * jj + 3]);
+        }
+        fence_acq_rel_cluster();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(partial_full), peer));
+        // the peer's sums for this CTA's half
+        bool got = true;
+        if (lane == 0) {
+          const uint64_t t0 = global_timer_ns();
+          while (!mbar_try_wait_cluster(partial_full, 0)) {
+            if (*abort_flag || global_timer_ns() - t0 > p.wait_limit_ns) {
+              *abort_flag = 1u;
+              if (p.status) atomicMax(p.status, (uint32_t)ST_TIMEOUT_EPILOGUE);
+              got = false;
+              break;
             }
           }
-          got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
-          if (!got) break;
-          fence_acq_rel_cluster();
-        } else {
-          // wait until CTA 0 has finished with its stages, then send this CTA's accumulators and leave
-          if (!mbar_wait_warp(stages_free, 0, ctl, ST_TIMEOUT_EPILOGUE)) break;
-          const uint32_t dst_row = mapa_u32(part_row, 0);
-#pragma unroll 1
-          for (int c = 0; c < (t.bn >> 5); ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(taddr_s + c * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              st_cluster_v4(dst_row + (uint32_t)((c * 8 + j) * 128 * 16), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-          }
-          fence_acq_rel_cluster();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(partial_full), 0));
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tempty[buf]);
-          continue;
         }
+        got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+        if (!got) break;
+        fence_acq_rel_cluster();
+        c_begin = crank * half_chunks;
+        c_end = c_begin + half_chunks;
       }
       const size_t row_off = ((size_t)t.bA * p.M + (row_ok ? m : 0)) * (size_t)p.N;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-      const int chunks = t.bn >> 5;
+      const int chunks = c_end;
       // Whole row blocks go out as tiled bulk stores (coalesced, clipped at the tensor's edge); a partial
       // block of the grouped form must not touch the rows after it and uses per-row stores.
       const bool tma_out = p.tma_store != 0 && (p.meta == nullptr || t.rows == W8_BM);
       uint32_t r[2][32];
-      tmem_ld_32x32b_x32(taddr, r[0]);
+      tmem_ld_32x32b_x32(taddr + c_begin * 32, r[0]);
 #pragma unroll 1
-      for (int c2 = 0; c2 < chunks; c2 += 2) {
+      for (int c2 = c_begin; c2 < chunks; c2 += 2) {
         if (tma_out) {  // the previous bulk store has read the staging tile
           if (lane == 0) bulk_wait_group_read0();
           __syncwarp();
@@ -375,7 +379,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               uint4 pv;
               asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                            : "=r"(pv.x), "=r"(pv.y), "=r"(pv.z), "=r"(pv.w)
-                           : "r"(part_row + (uint32_t)((c * 8 + j) * 128 * 16)));
+                           : "r"(part_row + (uint32_t)(((c - c_begin) * 8 + j) * 128 * 16)));
               r[h][4 * j] += pv.x;
               r[h][4 * j + 1] += pv.y;
               r[h][4 * j + 2] += pv.z;
