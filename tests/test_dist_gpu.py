@@ -41,11 +41,13 @@ def _worker(rank, world, port, q):
                 out = peer(A.cuda())
                 torch.cuda.synchronize()
                 good = torch.allclose(out.cpu().float(), ref.float(), rtol=1e-2, atol=1e-2)
-                same = torch.equal(out, coll(A.cuda()))
+                # the two forms may cut a tile's K differently (one launch over a cluster / two launches over the
+                # persistent grid), i.e. add the same fp32 partial sums in another order
+                same = torch.allclose(out.float(), coll(A.cuda()).float(), rtol=2e-3, atol=2e-3)
                 if not (good and same and out.shape == (M, N)):
                     ok, msg = False, f"M={M} {dt} rep {rep}: close to oracle {good}, equal to collective form {same}"
             loc = peer.forward(A.cuda(), gather=False)
-            if not torch.equal(loc, out[:, peer.n0:peer.n1]):
+            if not torch.allclose(loc.float(), out[:, peer.n0:peer.n1].float(), rtol=2e-3, atol=2e-3):
                 ok, msg = False, f"M={M}: local block differs from the gathered columns"
         # the all-reduce form of the "landed" barrier gives the same bits
         peer_ar = ColumnShardedW4A16(P, S, 8, 128, peer_stores=True, landed="allreduce").to("cuda")

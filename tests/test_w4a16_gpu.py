@@ -341,8 +341,11 @@ def test_kernels_on_either_side_of_a_switch_agree():
     ref = oc.dequant_gemm_fp16_ref(A, packed, "float16", scales, 8, 128)
     _close(C65, ref)
     _close(C64, ref[:64])
-    # the group-sum kernel does the same arithmetic per row whatever the token count and tile height
-    assert torch.equal(C32, C64[:32]) and torch.equal(C8, C64[:8])
+    # the group-sum kernel does the same arithmetic per row whatever the token count and tile height ...
+    assert torch.equal(C32, C64[:32])
+    # ... up to the order in which the K ranges of a split tile are added in fp32 (the single-launch form of small
+    # problems cuts K over a cluster, the two-launch form over the persistent grid)
+    torch.testing.assert_close(C8.float(), C64[:8].float(), rtol=2e-3, atol=2e-3)
     # |sum_k a w (1 + e_k)| with |e_k| <= 2^-11: bounded by 2^-11 * sum |a w|, plus the output's own rounding
     W = oc.dequant_weight_ref(packed, scales, 8, 128).float()
     bound = (A.float().abs() @ W.abs().t()) * 2.0 ** -11 + ref.float().abs() * 2.0 ** -9 + 1e-3
@@ -425,3 +428,38 @@ def test_back_to_back_calls_that_feed_each_other():
         ref = oc.dequant_gemm_fp16_ref(x, P, "float16", S, 8, 128)
         _close(c, ref)
         x = c.cpu()
+
+
+SMALL_SHAPES = [
+    # M, K, N, group, dtype, batch: clusters of 1 (K <= 1024), 2, 4 and 8 CTAs, ragged N, fewer than 16 tokens, batches
+    (16, 1024, 256, 128, "float16", None), (5, 512, 136, 128, "bfloat16", None), (16, 2048, 512, 128, "float16", None),
+    (9, 4096, 1024, 128, "bfloat16", None), (16, 4096, 4096, 128, "float16", None), (1, 8192, 2048, 128, "float16", None),
+    (16, 8192, 2304, 256, "bfloat16", None), (12, 4096, 264, 4096, "float16", None), (16, 2048, 384, 128, "float16", 3),
+]
+
+
+@pytest.mark.parametrize("M,K,N,group,dt,batch", SMALL_SHAPES)
+def test_single_launch_form_of_small_problems(M, K, N, group, dt, batch):
+    """Problems of at most four slabs per CTA run as one launch (activations prepared inside the kernel, K cut over a
+    thread-block cluster whose CTAs add their sums through distributed shared memory): results against the oracle,
+    one-hot rows bit for bit, the interleaved layout identical, and two runs identical."""
+    q = _q()
+    if batch is None:
+        A, P, S = oc.make_w4a16_inputs(M, K, N, dt, group, seed=M + N)
+        ref = oc.dequant_gemm_fp16_ref(A, P, dt, S, 8, group)
+    else:
+        parts = [oc.make_w4a16_inputs(M, K, N, dt, group, seed=40 + i) for i in range(batch)]
+        A, P, S = [torch.stack([p[i] for p in parts]) for i in range(3)]
+        ref = torch.stack([oc.dequant_gemm_fp16_ref(*p[:2], dt, p[2], 8, group) for p in parts])
+    C = q.w4a16_gemm(A.cuda(), P.cuda(), S.cuda(), 8, group)
+    _close(C, ref)
+    assert torch.equal(C, q.w4a16_gemm(A.cuda(), P.cuda(), S.cuda(), 8, group))
+    if batch is None:
+        Pi = q.interleave_weight(P, 4, "float16").view(torch.uint8)
+        assert torch.equal(C, q.w4a16_gemm(A.cuda(), Pi.cuda(), S.cuda(), 8, group, weight_layout="interleaved"))
+        W = oc.dequant_weight_ref(P, S, 8, group)
+        for k0 in (0, K // 2 - 3, K - M):
+            hot = torch.zeros((M, K), dtype=A.dtype)
+            hot[torch.arange(M), k0 + torch.arange(M)] = 1
+            Wt = q.w4a16_gemm(hot.cuda(), P.cuda(), S.cuda(), 8, group, out_dtype=torch.float16)
+            assert torch.equal(Wt.cpu(), W[:, k0:k0 + M].t().contiguous())

@@ -102,6 +102,10 @@ int set_smem_w4g() {
   if (set_smem(qg::w4a16_gs_kernel<MT, true, true>, C::SMEM_BYTES)) return -1;
   if (set_smem(qg::w4a16_gs_kernel<MT, false, false, true>, C::SMEM_BYTES)) return -1;
   if (set_smem(qg::w4a16_gs_kernel<MT, true, false, true>, C::SMEM_BYTES)) return -1;
+  if constexpr (MT == 16) {
+    if (set_smem(qg::w4a16_gs_kernel<16, false, false, false, true>, C::SMEM_BYTES)) return -1;
+    if (set_smem(qg::w4a16_gs_kernel<16, true, false, false, true>, C::SMEM_BYTES)) return -1;
+  }
   return 0;
 }
 
@@ -246,6 +250,32 @@ int launch_w4g(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CU
   }
   if (bf) return launch_pdl(qg::w4a16_gs_kernel<MT, true>, grid, qg::W4G_THREADS, smem, s, tmW, tmS, tmS, tmA, p, dbg);
   return launch_pdl(qg::w4a16_gs_kernel<MT, false>, grid, qg::W4G_THREADS, smem, s, tmW, tmS, tmS, tmA, p, dbg);
+}
+
+// Single-launch form of the group-sum kernel (see its SMALL parameter): clusters of `cluster` CTAs, one tile per cluster,
+// no pre-pass in front.  Still a programmatic dependent of whatever is in front of it on the stream.
+int launch_w4g_small(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmA,
+                     const qg::W4A16Params& p, int grid, int cluster, cudaStream_t s) {
+  static const int pdl = getenv("QGEMM_PDL") ? atoi(getenv("QGEMM_PDL")) : 1;
+  qg::W4GDebug dbg;
+  dbg.withhold_last_commit = 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)qg::W4G_THREADS);
+  cfg.dynamicSmemBytes = (size_t)qg::W4GCfg<16>::SMEM_BYTES;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 2 : 1;
+  if (bf) CUDA_OK(cudaLaunchKernelEx(&cfg, qg::w4a16_gs_kernel<16, true, false, false, true>, tmW, tmS, tmS, tmA, p, dbg));
+  else CUDA_OK(cudaLaunchKernelEx(&cfg, qg::w4a16_gs_kernel<16, false, false, false, true>, tmW, tmS, tmS, tmA, p, dbg));
+  return 0;
 }
 
 // The group-sum kernel (w4a16_gs.cuh) serves up to 64 tokens when the scale groups are 128 wide, a multiple of
@@ -836,6 +866,8 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
   p.total_items = num_tiles * p.KS;
   p.status = status;
   p.wait_limit_ns = g_wait_limit_ns;
+  p.A_raw = nullptr;
+  p.a_is_bf16 = p.a_permute = 0;
   int64_t grid = sms < kW4MaxGrid ? sms : kW4MaxGrid;
   if (p.total_items < grid) grid = p.total_items;
   // Small problems (a few slabs per CTA): prefer a slightly smaller grid that cuts every tile into equal K ranges,
@@ -869,6 +901,23 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf = out_dtype == QGEMM_DT_BF16;
+  // Problems of a few slabs per CTA (16 tokens at most, every tile's K cut over a cluster of 1, 2, 4 or 8 CTAs with at
+  // most four slabs each, all clusters resident at once): one launch, no pre-pass, no scratch - see the kernel's SMALL
+  // parameter.  QGEMM_W4_SMALL=0 keeps the two-launch form.
+  {
+    static const int small_on = getenv("QGEMM_W4_SMALL") ? atoi(getenv("QGEMM_W4_SMALL")) : 1;
+    if (small_on && use_gs && mt == 16 && gd == nullptr && !zeros_inflight && !g_w4g_withhold_commit) {
+      int cluster = 0;
+      for (int c = 1; c <= 8; c *= 2)
+        if (p.KS % c == 0 && p.KS / c <= qg::W4G_SMALL_MAX_SLABS) { cluster = c; break; }
+      if (cluster > 0 && num_tiles * cluster <= sms) {
+        p.A_raw = A;
+        p.a_is_bf16 = a_dtype == QGEMM_DT_BF16 ? 1 : 0;
+        p.a_permute = weight_format == QGEMM_W4_SEQUENTIAL ? 1 : 0;
+        return launch_w4g_small(bf, tmW, tmS, tmA, p, (int)(num_tiles * cluster), cluster, s);
+      }
+    }
+  }
   {
     const long long n_chunks = (long long)batch * M * K / 8;
     const long long blocks = (n_chunks + 255) / 256;

@@ -44,6 +44,10 @@ struct W4A16Params {
   // Group-sum kernel only: tiles 0 .. sk_tiles - 1 are cut stream-K fashion over all CTAs, then CTA c takes dp_rounds
   // whole tiles sk_tiles + c + j * grid.  The other kernels deal all (tile, slab) items evenly (total_items).
   int sk_tiles, dp_rounds;
+  // Single-launch form of the group-sum kernel (no pre-pass): the caller's activations [batch, M, K], whether they
+  // are bf16, and whether every group of eight k is to be reordered (sequential weight layout).
+  const void* A_raw;
+  int a_is_bf16, a_permute;
   int scale_rows;       // scale rows fetched per slab (256 / group, at least 1)
   long long total_items;
   uint32_t* status;

@@ -76,6 +76,8 @@ constexpr int W4G_DRAIN = 832;
 constexpr int W4G_TMEM_SLOT = 840;
 constexpr int W4G_CTL = 848;          // u32 abort word (0, or the role code of the first wait that gave up), u32 max tries
 constexpr int W4G_EPI_CTRL = 856;     // u32[2], alternating by segment: bit 0 abort, bit 1 last contributor
+constexpr int W4G_PART_FULL = 864;    // SMALL form, in the cluster's first CTA: the other CTAs' sums have arrived
+constexpr int W4G_SMALL_MAX_SLABS = 4;  // SMALL form: slabs per CTA (stages 4.. of the raw ring receive the other CTAs' sums)
 
 template <int MT>
 struct W4GCfg {
@@ -209,7 +211,16 @@ struct W4HybridIter {
 // exact).  The weight producer fetches the slab's zero rows (through tmZ, laid out like the scale rows) into a ring
 // that shares the packed weights' stages and barriers, and a dequant thread builds its row's two magic constants
 // from the zero it reads there: five more instructions per 128-k half.
-template <int MT, bool OUT_BF16, bool GATHER = false, bool ZT = false>
+// SMALL = true (16-token tile): the single-launch form for problems of a few slabs per CTA.  The kernel is launched in
+// clusters of C = KS / (slabs per CTA) CTAs, one tile per cluster, CTA r taking the r-th K range; there is no pre-pass
+// and no scratch memory:
+//  - the drain warps first fetch the CTA's own piece of the activations straight from the caller's tensor, convert
+//    and reorder it as the pre-pass would, and write it into the activation stages in the layout the MMA descriptor
+//    expects (128-byte swizzle: 16-byte chunk j of row r of a 64-k block at chunk position j ^ (r & 7));
+//  - at the end CTAs 1 .. C-1 write their sums through distributed shared memory into the unused upper half of the
+//    first CTA's raw ring, and the first CTA adds them in rank order and writes the tile - no counters, no partial
+//    sums in global memory, the same fixed summation order on every run.
+template <int MT, bool OUT_BF16, bool GATHER = false, bool ZT = false, bool SMALL = false>
 __global__ void __launch_bounds__(W4G_THREADS, 1)
 w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmS,
                 const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmA, const W4A16Params p,
@@ -220,6 +231,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   constexpr int NSLOT = Cfg::NSLOT;
   constexpr int SS = W4G_SS;
   static_assert(RS == 8 && SS == 16 && AS <= 8 && NSLOT <= 8, "barrier block layout");
+  static_assert(!SMALL || (MT == 16 && !GATHER && !ZT), "the single-launch form: 16-token tile, one destination, scalar zero");
   // The next call's pre-pass (a programmatic dependent) may become resident now; it waits for this whole grid before
   // it touches anything, and the GEMM kernel behind it only reads weights and scales until that pre-pass is done.
   pdl_launch_dependents();
@@ -280,6 +292,11 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     tma_prefetch_desc(&tmA);
     if (p.has_scales) tma_prefetch_desc(&tmS);
     if (ZT) tma_prefetch_desc(&tmZ);
+    if constexpr (SMALL) {
+      const uint32_t others = cluster_nctarank() - 1u;
+      mbar_init(reinterpret_cast<uint64_t*>(bar_block + W4G_PART_FULL), others > 0u ? others : 1u);
+      fence_barrier_init();
+    }
   }
   if (warp == 2) {
     tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -288,6 +305,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  if constexpr (SMALL) cluster_sync_all();  // the first CTA's barrier exists before any other CTA of the cluster signals it
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_w = tmem_base + NSLOT * 2 * MT;  // converted weights behind the accumulator ring
   const uint32_t bar0 = smem_u32(bar_block);
@@ -300,14 +318,19 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   // sk_tiles + c, sk_tiles + c + G, ...  The hand-overs of the partial tiles thus happen early, behind the following
   // tiles' work, and the launch ends with plain tile writes.
   const long long T = (long long)p.sk_tiles * p.KS;  // stream-K items
-  const long long item0 = w4_range_begin(T, G, cta), item1 = w4_range_begin(T, G, cta + 1);
+  // SMALL: cluster t takes tile t, its CTA r the slabs [r * per, (r + 1) * per) of it
+  const int crank = SMALL ? (int)cluster_ctarank() : 0;
+  const int csize = SMALL ? (int)cluster_nctarank() : 1;
+  const int per = SMALL ? p.KS / csize : 0;
+  const long long item0 = SMALL ? (long long)(cta / csize) * p.KS + (long long)crank * per : w4_range_begin(T, G, cta);
+  const long long item1 = SMALL ? item0 + per : w4_range_begin(T, G, cta + 1);
   const int n_sk = (int)(item1 - item0);
-  const int n_slabs = n_sk + p.dp_rounds * p.KS;  // this CTA's slabs, numbered 0.. in processing order
+  const int n_slabs = SMALL ? n_sk : n_sk + p.dp_rounds * p.KS;  // this CTA's slabs, numbered 0.. in processing order
 
   if (warp <= 2) {
     // ------------------------------------------------------------------ TMA producers
     // warp 0: packed weights, warp 1: activations, warp 2: scales
-    if (lane == 0 && (warp != 2 || p.has_scales)) {
+    if (lane == 0 && (warp != 2 || p.has_scales) && !(SMALL && warp == 1)) {
       if (warp == 1) pdl_wait();  // the prepared activations come from the pre-pass kernel in front of this one
       uint64_t* full = warp == 0 ? raw_full : (warp == 1 ? a_full : sc_full);
       const uint32_t empty0 = bar0 + (warp == 0 ? W4G_RAW_EMPTY : (warp == 1 ? W4G_A_EMPTY : W4G_SC_EMPTY));
@@ -441,8 +464,52 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     const uint32_t sc_row1 = p.scale_rows == 2 ? 256u : 0u;  // the second half's scale row inside a stage
     const bool scaled = p.has_scales != 0;
     const bool lead = lane == 0;
-    pdl_wait();  // the arrival counters are zeroed by the pre-pass kernel in front of this one
-    W4HybridIter seg{W4SegIter{item0, item1, p.KS}, p.sk_tiles + cta, p.dp_rounds, G, p.KS};
+    pdl_wait();  // the arrival counters are zeroed by the pre-pass kernel in front of this one (SMALL: whatever is in
+                 // front of this launch has finished, so the activations and the output may be touched)
+    if constexpr (SMALL) {
+      // this CTA's piece of the activations: rows m0 .. m0 + 15 (zero beyond M), k [256 * ks_first, 256 * (ks_first + per))
+      const int tile_s = (int)(item0 / p.KS);
+      const int ks_first = (int)(item0 - (long long)tile_s * p.KS);
+      int bb, nn0, mm0;
+      w4_tile_coords(p, tile_s, MT, bb, nn0, mm0);
+      const int tid = (e * 4 + q) * 32 + lane;  // 0 .. 255
+      const int chunks_per_row = per * 32;       // 16-byte chunks (eight k) per row in this CTA's K range
+      const uint4* src = reinterpret_cast<const uint4*>(p.A_raw) + ((size_t)bb * p.M) * (size_t)(p.K / 8);
+      const int row_chunks = p.K / 8;  // chunks in a whole row of A: the last slab of a short K is partly outside
+      constexpr int PER_THREAD = MT * W4G_SMALL_MAX_SLABS * 32 / 256;  // at most eight chunks per thread
+      uint4 v[PER_THREAD];
+#pragma unroll
+      for (int u = 0; u < PER_THREAD; ++u) {  // all loads first, so that their latencies overlap
+        const int c = tid + 256 * u;
+        const int r = c / chunks_per_row, kc = c - r * chunks_per_row;
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (c < MT * chunks_per_row && mm0 + r < p.M && ks_first * 32 + kc < row_chunks)
+          v[u] = __ldg(src + (size_t)(mm0 + r) * (size_t)row_chunks + (size_t)ks_first * 32 + kc);
+      }
+#pragma unroll
+      for (int u = 0; u < PER_THREAD; ++u) {
+        const int c = tid + 256 * u;
+        if (c < MT * chunks_per_row) {
+          const int r = c / chunks_per_row, kc = c - r * chunks_per_row;
+          uint4 w = v[u];
+          if (p.a_is_bf16) {
+            w.x = w4_bf16x2_to_f16x2(w.x);
+            w.y = w4_bf16x2_to_f16x2(w.y);
+            w.z = w4_bf16x2_to_f16x2(w.z);
+            w.w = w4_bf16x2_to_f16x2(w.w);
+          }
+          if (p.a_permute) w = w4_permute_act(w);
+          const int slab = kc >> 5, j = kc & 31;  // chunk j of the slab: 64-k block j / 8, chunk j % 8 of the row there
+          uint8_t* dst = a_base + slab * Cfg::A_BYTES + (j >> 3) * Cfg::A_KB_BYTES + r * 128 + (((j & 7) ^ (r & 7)) << 4);
+          *reinterpret_cast<uint4*>(dst) = w;
+        }
+      }
+      fence_proxy_async_smem();  // the MMAs read these stages through the async proxy
+      w4g_epi_bar();
+      if (tid == 0)
+        for (int sidx = 0; sidx < per; ++sidx) mbar_arrive(&a_full[sidx]);
+    }
+    W4HybridIter seg{W4SegIter{item0, item1, p.KS}, p.sk_tiles + cta, SMALL ? 0 : p.dp_rounds, G, p.KS};
     int tile, ks0, ks1;
     uint32_t i_seg0 = 0;  // CTA-local index of the segment's first slab
     uint32_t fail = 0;
@@ -526,6 +593,57 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
         for (int j = 0; j < DT; ++j) xb[j * W4_BN] = psum[j];
       }
       w4g_epi_bar();
+      if constexpr (SMALL) {
+        // One segment per CTA.  Set 0 holds the CTA's sums; CTAs 1 .. C-1 of the cluster write theirs into the first
+        // CTA's landing area (the raw ring's stages 4 .. 7, never filled in this form) and signal it; the first CTA
+        // adds them in rank order and writes the tile.
+        if (e == 0) {
+#pragma unroll
+          for (int j = 0; j < DT; ++j) psum[j] += xb[j * W4_BN];
+        }
+        float* landing = reinterpret_cast<float*>(raw_base + W4G_SMALL_MAX_SLABS * W4_RAW_PACKED);  // [rank - 1][token][row]
+        if (crank != 0) {
+          if (e == 0 && !fail) {
+            const uint32_t dst = mapa_u32(smem_u32(landing + (size_t)(crank - 1) * (MT * W4_BN) + nl), 0);
+#pragma unroll
+            for (int j = 0; j < DT; ++j)
+              asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst + (uint32_t)(j * W4_BN * 4)), "f"(psum[j]) : "memory");
+            fence_acq_rel_cluster();
+          }
+          w4g_epi_bar();  // every thread's stores are issued and fenced before the one signal
+          if (warp == W4G_FIRST_EPI_WARP && lane == 0 && !fail && ctl_words[0] == 0)
+            mbar_arrive_cluster(mapa_u32(bar0 + W4G_PART_FULL, 0));
+        } else {
+          bool got = true;
+          if (csize > 1) {
+            if (lane == 0) {
+              const uint64_t t0 = global_timer_ns();
+              while (!mbar_try_wait_cluster(reinterpret_cast<uint64_t*>(bar_block + W4G_PART_FULL), 0)) {
+                if (ctl_words[0] != 0 || global_timer_ns() - t0 > p.wait_limit_ns) {
+                  if (ctl_words[0] == 0) ctl_words[0] = ST_TIMEOUT_EPILOGUE;
+                  got = false;
+                  break;
+                }
+              }
+            }
+            got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+            fence_acq_rel_cluster();
+          }
+          if (got && e == 0 && !fail && n < p.N) {
+            for (int c = 1; c < csize; ++c) {
+              const float* src = landing + (size_t)(c - 1) * (MT * W4_BN) + nl;
+#pragma unroll
+              for (int j = 0; j < DT; ++j) psum[j] += src[j * W4_BN];
+            }
+#pragma unroll
+            for (int j = 0; j < DT; ++j) {
+              const int m = m0 + j;
+              if (m < p.M) w4_store_out<OUT_BF16, GATHER>(p, Cout, m, n, psum[j]);
+            }
+          }
+        }
+        break;
+      }
       const long long first_item = (long long)tile * p.KS;
       int b_first = 0, b_last = 0;
       if (!full_tile) {
@@ -694,6 +812,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
   // ------------------------------------------------------------------ teardown
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (SMALL) cluster_sync_all();  // no CTA of the cluster leaves while another may still reach into it
   if (warp == 2) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
