@@ -464,8 +464,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
     const uint32_t sc_row1 = p.scale_rows == 2 ? 256u : 0u;  // the second half's scale row inside a stage
     const bool scaled = p.has_scales != 0;
     const bool lead = lane == 0;
-    pdl_wait();  // the arrival counters are zeroed by the pre-pass kernel in front of this one (SMALL: whatever is in
-                 // front of this launch has finished, so the activations and the output may be touched)
+    if constexpr (!SMALL) pdl_wait();  // the arrival counters are zeroed by the pre-pass kernel in front of this one
     if constexpr (SMALL) {
       // this CTA's piece of the activations: rows m0 .. m0 + 15 (zero beyond M), k [256 * ks_first, 256 * (ks_first + per))
       const int tile_s = (int)(item0 / p.KS);
@@ -477,20 +476,27 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
       const uint4* src = reinterpret_cast<const uint4*>(p.A_raw) + ((size_t)bb * p.M) * (size_t)(p.K / 8);
       const int row_chunks = p.K / 8;  // chunks in a whole row of A: the last slab of a short K is partly outside
       constexpr int PER_THREAD = MT * W4G_SMALL_MAX_SLABS * 32 / 256;  // at most eight chunks per thread
-      uint4 v[PER_THREAD];
-#pragma unroll
-      for (int u = 0; u < PER_THREAD; ++u) {  // all loads first, so that their latencies overlap
-        const int c = tid + 256 * u;
-        const int r = c / chunks_per_row, kc = c - r * chunks_per_row;
-        v[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (c < MT * chunks_per_row && mm0 + r < p.M && ks_first * 32 + kc < row_chunks)
-          v[u] = __ldg(src + (size_t)(mm0 + r) * (size_t)row_chunks + (size_t)ks_first * 32 + kc);
-      }
+      const uint4* ptr[PER_THREAD];
+      uint32_t dst_off[PER_THREAD];  // byte offset in the activation stages, or ~0 for a chunk this thread does not have
 #pragma unroll
       for (int u = 0; u < PER_THREAD; ++u) {
         const int c = tid + 256 * u;
-        if (c < MT * chunks_per_row) {
-          const int r = c / chunks_per_row, kc = c - r * chunks_per_row;
+        const int r = c / chunks_per_row, kc = c - r * chunks_per_row;
+        const int slab = kc >> 5, j = kc & 31;  // chunk j of the slab: 64-k block j / 8, chunk j % 8 of the row there
+        dst_off[u] = c < MT * chunks_per_row
+                         ? (uint32_t)(slab * Cfg::A_BYTES + (j >> 3) * Cfg::A_KB_BYTES + r * 128 + (((j & 7) ^ (r & 7)) << 4))
+                         : 0xffffffffu;
+        const bool inside = c < MT * chunks_per_row && mm0 + r < p.M && ks_first * 32 + kc < row_chunks;
+        ptr[u] = inside ? src + (size_t)(mm0 + r) * (size_t)row_chunks + (size_t)ks_first * 32 + kc : nullptr;
+      }
+      pdl_wait();  // whatever is in front of this launch has finished: the activations may be read, the output written
+      uint4 v[PER_THREAD];
+#pragma unroll
+      for (int u = 0; u < PER_THREAD; ++u)  // all loads first, so that their latencies overlap
+        v[u] = ptr[u] != nullptr ? __ldcg(ptr[u]) : make_uint4(0u, 0u, 0u, 0u);  // L2 is the point of coherence
+#pragma unroll
+      for (int u = 0; u < PER_THREAD; ++u) {
+        if (dst_off[u] != 0xffffffffu) {
           uint4 w = v[u];
           if (p.a_is_bf16) {
             w.x = w4_bf16x2_to_f16x2(w.x);
@@ -499,9 +505,7 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             w.w = w4_bf16x2_to_f16x2(w.w);
           }
           if (p.a_permute) w = w4_permute_act(w);
-          const int slab = kc >> 5, j = kc & 31;  // chunk j of the slab: 64-k block j / 8, chunk j % 8 of the row there
-          uint8_t* dst = a_base + slab * Cfg::A_BYTES + (j >> 3) * Cfg::A_KB_BYTES + r * 128 + (((j & 7) ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = w;
+          *reinterpret_cast<uint4*>(a_base + dst_off[u]) = w;
         }
       }
       fence_proxy_async_smem();  // the MMAs read these stages through the async proxy
