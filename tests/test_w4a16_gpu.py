@@ -431,7 +431,7 @@ def test_back_to_back_calls_that_feed_each_other():
 
 
 SMALL_SHAPES = [
-    # M, K, N, group, dtype, batch: clusters of 1 (K <= 1024), 2, 4 and 8 CTAs, ragged N, fewer than 16 tokens, batches
+    # M, K, N, group, dtype, batch: clusters of 1 (K <= 1024), 2 and 4 CTAs, K beyond the form's range, ragged N, batches
     (16, 1024, 256, 128, "float16", None), (5, 512, 136, 128, "bfloat16", None), (16, 2048, 512, 128, "float16", None),
     (9, 4096, 1024, 128, "bfloat16", None), (16, 4096, 4096, 128, "float16", None), (1, 8192, 2048, 128, "float16", None),
     (16, 8192, 2304, 256, "bfloat16", None), (12, 4096, 264, 4096, "float16", None), (16, 2048, 384, 128, "float16", 3),

@@ -901,16 +901,18 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf = out_dtype == QGEMM_DT_BF16;
-  // Problems of a few slabs per CTA (16 tokens at most, every tile's K cut over a cluster of 1, 2, 4 or 8 CTAs with at
-  // most four slabs each, all clusters resident at once): one launch, no pre-pass, no scratch - see the kernel's SMALL
-  // parameter.  QGEMM_W4_SMALL=0 keeps the two-launch form.
+  // Problems of a few slabs per CTA (16 tokens at most, K <= 4096: every tile's K cut over a cluster of 1, 2 or 4 CTAs
+  // with at most four slabs each, all clusters resident at once): one launch, no pre-pass, no scratch - see the
+  // kernel's SMALL parameter.  Measured against the two-launch form: 16 x 4096 x 4096 9.2 / 10.6 us, 16 x 2048 x 8192
+  // 8.8 / 9.8 us; with more clusters than SMs (several waves) it loses.  QGEMM_W4_SMALL=0 keeps the two-launch form.
   {
     static const int small_on = getenv("QGEMM_W4_SMALL") ? atoi(getenv("QGEMM_W4_SMALL")) : 1;
     if (small_on && use_gs && mt == 16 && gd == nullptr && !zeros_inflight && !g_w4g_withhold_commit) {
       int cluster = 0;
-      for (int c = 1; c <= 8; c *= 2)
+      for (int c = 1; c <= 4; c *= 2)  // clusters of eight were measured slower than the two-launch form (15.3 / 11.3 us)
         if (p.KS % c == 0 && p.KS / c <= qg::W4G_SMALL_MAX_SLABS) { cluster = c; break; }
-      if (cluster > 0 && num_tiles * cluster <= sms) {
+      static const int small_waves = getenv("QGEMM_W4_SMALL_WAVES") ? atoi(getenv("QGEMM_W4_SMALL_WAVES")) : 1;
+      if (cluster > 0 && num_tiles * cluster <= (int64_t)small_waves * sms) {
         p.A_raw = A;
         p.a_is_bf16 = a_dtype == QGEMM_DT_BF16 ? 1 : 0;
         p.a_permute = weight_format == QGEMM_W4_SEQUENTIAL ? 1 : 0;
