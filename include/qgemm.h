@@ -60,11 +60,12 @@ const char* qgemm_last_error(void);
 /* Per-wait limit of the kernels' bounded waits, in milliseconds (default 2000). */
 void qgemm_set_wait_limit_ms(uint32_t ms);
 
-/* Test hook, off by default (no counterpart in the reference).  While on, the W4A16 kernel for 9..32
- * tokens leaves one accumulator hand-over of the launch unsignalled, so that one bounded wait of its
- * epilogue runs out: the launch then ends after the wait limit with QGEMM_ST_TIMEOUT_EPILOGUE in `status`
- * and an unspecified C, nothing is left in flight and the next call works normally.  It exists so that a
- * test can see the time-out path end to end without faulting or hanging the device. */
+/* Test hook, off by default (no counterpart in the reference).  With 1 the small-token W4A16 kernel (two-launch
+ * form) leaves one accumulator hand-over of the launch unsignalled; with 2 the single-launch form of small problems
+ * keeps back one CTA's "my sums have arrived" signal inside the last cluster.  Either way one bounded wait of the
+ * epilogue runs out: the launch ends after the wait limit with QGEMM_ST_TIMEOUT_EPILOGUE in `status` and an
+ * unspecified C, nothing is left in flight and the next call works normally.  It exists so that a test can see the
+ * time-out paths end to end without faulting or hanging the device. */
 void qgemm_debug_withhold_commit(int on);
 
 /*

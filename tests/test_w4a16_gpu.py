@@ -463,3 +463,31 @@ def test_single_launch_form_of_small_problems(M, K, N, group, dt, batch):
             hot[torch.arange(M), k0 + torch.arange(M)] = 1
             Wt = q.w4a16_gemm(hot.cuda(), P.cuda(), S.cuda(), 8, group, out_dtype=torch.float16)
             assert torch.equal(Wt.cpu(), W[:, k0:k0 + M].t().contiguous())
+
+
+def test_single_launch_form_gives_up_cleanly_when_a_cluster_signal_is_missing():
+    """The bounded wait of the single-launch form, made to expire in the safe way: with the test hook at 2, CTA 1 of
+    the last cluster writes its sums but keeps its signal back, so the first CTA's wait runs into the limit (20 ms).
+    The kernel must return by itself with QGEMM_ST_TIMEOUT_EPILOGUE, and the next ordinary call must be exact."""
+    q = _q()
+    from tilelang_ascend_b200 import _lib
+    lib = _lib.load()
+    A, packed, scales = oc.make_w4a16_inputs(16, 4096, 512, "float16", 128, seed=9)  # four clusters of four CTAs
+    Ad, Pd, Sd = A.cuda(), packed.cuda(), scales.cuda()
+    ref = oc.dequant_gemm_fp16_ref(A, packed, "float16", scales, 8, 128)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    try:
+        lib.qgemm_set_wait_limit_ms(20)
+        lib.qgemm_debug_withhold_commit(2)
+        C_bad = q.w4a16_gemm(Ad, Pd, Sd, 8, 128, status=status)
+        torch.cuda.synchronize()  # returns: the kernel gave up by itself
+        assert int(status.item()) == 3  # QGEMM_ST_TIMEOUT_EPILOGUE
+        # the clusters whose signals all arrived wrote their tiles
+        _close(C_bad[:, :384], ref[:, :384])
+    finally:
+        lib.qgemm_debug_withhold_commit(0)
+        lib.qgemm_set_wait_limit_ms(2000)
+    status.zero_()
+    C = q.w4a16_gemm(Ad, Pd, Sd, 8, 128, status=status)
+    _close(C, ref)
+    assert int(status.item()) == 0

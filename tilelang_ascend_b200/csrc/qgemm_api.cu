@@ -258,7 +258,7 @@ int launch_w4g_small(bool bf, const CUtensorMap& tmW, const CUtensorMap& tmS, co
                      const qg::W4A16Params& p, int grid, int cluster, cudaStream_t s) {
   static const int pdl = getenv("QGEMM_PDL") ? atoi(getenv("QGEMM_PDL")) : 1;
   qg::W4GDebug dbg;
-  dbg.withhold_last_commit = 0;
+  dbg.withhold_last_commit = g_w4g_withhold_commit;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3((unsigned)qg::W4G_THREADS);
@@ -449,7 +449,7 @@ const char* qgemm_last_error(void) { return g_err; }
 
 void qgemm_set_wait_limit_ms(uint32_t ms) { g_wait_limit_ns = (unsigned long long)ms * 1000000ull; }
 
-void qgemm_debug_withhold_commit(int on) { g_w4g_withhold_commit = on ? 1 : 0; }
+void qgemm_debug_withhold_commit(int on) { g_w4g_withhold_commit = (on == 2) ? 2 : (on ? 1 : 0); }
 
 int qgemm_init(void) {
   int sms = 0;
@@ -907,7 +907,7 @@ static int w4a16_impl(const void* A, const uint8_t* B_packed, const void* scales
   // 8.8 / 9.8 us; with more clusters than SMs (several waves) it loses.  QGEMM_W4_SMALL=0 keeps the two-launch form.
   {
     static const int small_on = getenv("QGEMM_W4_SMALL") ? atoi(getenv("QGEMM_W4_SMALL")) : 1;
-    if (small_on && use_gs && mt == 16 && gd == nullptr && !zeros_inflight && !g_w4g_withhold_commit) {
+    if (small_on && use_gs && mt == 16 && gd == nullptr && !zeros_inflight && g_w4g_withhold_commit != 1) {
       int cluster = 0;
       for (int c = 1; c <= 4; c *= 2)  // clusters of eight were measured slower than the two-launch form (15.3 / 11.3 us)
         if (p.KS % c == 0 && p.KS / c <= qg::W4G_SMALL_MAX_SLABS) { cluster = c; break; }

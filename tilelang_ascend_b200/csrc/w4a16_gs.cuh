@@ -105,7 +105,7 @@ struct W4GCfg {
 // the last 128-k half of the launch, so the drain warps' wait for it runs out.  Nothing else is affected:
 // every copy lands, every other barrier completes, the kernel frees its tensor memory and returns.
 struct W4GDebug {
-  int withhold_last_commit;
+  int withhold_last_commit;  // 1: as described above (two-launch form); 2: the single-launch form's cluster signal
 };
 
 // ---- lean primitives on shared-space addresses ------------------------------------------------------
@@ -615,7 +615,9 @@ w4a16_gs_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
             fence_acq_rel_cluster();
           }
           w4g_epi_bar();  // every thread's stores are issued and fenced before the one signal
-          if (warp == W4G_FIRST_EPI_WARP && lane == 0 && !fail && ctl_words[0] == 0)
+          // (test hook, value 2: the last cluster's CTA 1 keeps its signal back, so that the first CTA's wait runs out)
+          const bool withheld = dbg.withhold_last_commit == 2 && crank == 1 && cta / csize == G / csize - 1;
+          if (warp == W4G_FIRST_EPI_WARP && lane == 0 && !fail && ctl_words[0] == 0 && !withheld)
             mbar_arrive_cluster(mapa_u32(bar0 + W4G_PART_FULL, 0));
         } else {
           bool got = true;
