@@ -175,3 +175,18 @@ def test_shard_groups_covers_all_rows():
 def test_group_sharded_w8a8_two_ranks():
     res = _run(_worker_group_shard)
     assert all(ok for _, ok, _ in res), res
+
+
+def test_column_sharded_layer_argument_checks():
+    """Host-side validation: the form of the "landed" signal must be one of the two known ones, layers that share
+    output buffers must have the same output width, and on CPU tensors the layer falls back to the collective form."""
+    _, P, S = oc.make_w4a16_inputs(1, 256, 256, "float16", 128, seed=3)
+    with pytest.raises(ValueError, match="landed"):
+        ColumnShardedW4A16(P, S, 8, 128, gemm=_cpu_gemm, landed="carrier pigeon")
+    a = ColumnShardedW4A16(P, S, 8, 128, gemm=_cpu_gemm)
+    _, P2, S2 = oc.make_w4a16_inputs(1, 256, 384, "float16", 128, seed=4)
+    with pytest.raises(ValueError, match="same N"):
+        ColumnShardedW4A16(P2, S2, 8, 128, gemm=_cpu_gemm, share_buffers_with=a)
+    A, _, _ = oc.make_w4a16_inputs(4, 256, 256, "float16", 128, seed=5)
+    assert not a._use_peers(A)  # CPU tensors, custom GEMM: never the peer-store form
+    assert a.forward(A).shape == (4, 256)
